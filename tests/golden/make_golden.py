@@ -1,0 +1,246 @@
+"""Generate golden vectors by running the reference's own selection code on CPU.
+
+Run in a container that has the reference checkout (it cannot travel):
+
+    python tests/golden/make_golden.py --reference /root/reference
+
+The reference's ``AttentionSharing.get_active_blocks`` / ``update_pivotal_attns``
+(shareprefill/attn/attention_sharing.py:94-366) and their helpers
+(shareprefill/attn/utils.py) run unmodified.  Three things are supplied from the
+outside, none touching reference files:
+
+* the literal device string ``"cuda"`` in ``torch.empty(..., device="cuda")`` and
+  ``Tensor.to("cuda")`` is mapped to CPU while the reference runs;
+* ``triton_bnhd_pool`` (a Triton kernel) is rebound to a torch block mean;
+* the block-sparse attention kernel (Triton, GPU only) is replaced by the oracle's
+  restatement, which is what feeds ``avg_attn`` into ``update_pivotal_attns``.
+  The ``avg_attn`` matrices stored here are therefore oracle outputs, not reference
+  outputs; everything else in the files is reference output.
+
+Stage-boundary tensors are captured by wrapping the helper names inside the
+``attention_sharing`` module namespace (it imports them by name, :23-32).
+"""
+from __future__ import annotations
+
+import argparse
+import contextlib
+import hashlib
+import json
+import math
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import spf_oracle as orc  # noqa: E402
+from shareprefill_b200.workloads import AttentionWorkload, make_qkv, synthetic_lookup  # noqa: E402
+
+
+def tensor_digest(*ts) -> str:
+    hsh = hashlib.sha256()
+    for t in ts:
+        hsh.update(t.contiguous().view(torch.uint8).numpy().tobytes())
+    return hsh.hexdigest()
+
+
+@contextlib.contextmanager
+def cuda_string_to_cpu():
+    real_empty, real_to = torch.empty, torch.Tensor.to
+
+    def empty(*a, **kw):
+        if kw.get("device") == "cuda":
+            kw["device"] = "cpu"
+        return real_empty(*a, **kw)
+
+    def to(self, *a, **kw):
+        a = tuple("cpu" if (isinstance(x, str) and x == "cuda") else x for x in a)
+        if kw.get("device") == "cuda":
+            kw["device"] = "cpu"
+        return real_to(self, *a, **kw)
+
+    torch.empty, torch.Tensor.to = empty, to
+    try:
+        yield
+    finally:
+        torch.empty, torch.Tensor.to = real_empty, real_to
+
+
+CASES = {
+    # name: (workload, lookup kwargs, layers, description)
+    "peaky_share": dict(
+        wl=AttentionWorkload("peaky_share", 90, 1024, 4, 2, head_dim=64, num_layers=3,
+                             num_head_clusters=2, shared_rank=4, block_size=64, min_budget=128,
+                             pattern_threshold=0.9, fallback_threshold=1e9, q_gain=3.0),
+        lookup=dict(num_clusters=2, shared=[0, 1]),
+    ),
+    "peaky_default": dict(
+        wl=AttentionWorkload("peaky_default", 91, 2048, 8, 2, head_dim=128, num_layers=3,
+                             num_head_clusters=2, shared_rank=4, block_size=128, min_budget=256,
+                             pattern_threshold=0.95, q_gain=2.5),
+        lookup=dict(num_clusters=2, shared=[1]),
+    ),
+    "diffuse_qa": dict(
+        wl=AttentionWorkload("diffuse_qa", 92, 2048, 8, 2, head_dim=128, num_layers=2,
+                             num_head_clusters=2, shared_rank=4, block_size=128, min_budget=256,
+                             pattern_threshold=0.95, queryaware_threshold=0.3),
+        lookup=dict(num_clusters=2, shared=[0, 1]),
+    ),
+    "ragged_rope": dict(
+        wl=AttentionWorkload("ragged_rope", 93, 1000, 6, 2, head_dim=64, num_layers=3,
+                             num_head_clusters=2, shared_rank=4, block_size=64, min_budget=192,
+                             rope_theta=500000.0, pattern_threshold=0.9, fallback_threshold=1e9,
+                             q_gain=2.0, similarity_threshold=0.9),
+        lookup=dict(num_clusters=2, shared=[0]),
+    ),
+}
+
+
+def run_case(name, spec, refmod):
+    wl: AttentionWorkload = spec["wl"]
+    lookup = synthetic_lookup(wl.num_layers, wl.num_q_heads, group_size=wl.group_size, **spec["lookup"])
+    lookup_path = os.path.join(HERE, f"_{name}_lookup.json")
+    with open(lookup_path, "w") as f:
+        json.dump(lookup, f)
+    att = refmod
+    ref_state = att.AttentionSharing(lookup_path)
+    os.remove(lookup_path)
+
+    bs, nb = wl.block_size, wl.num_blocks
+    mb = math.ceil(wl.min_budget / bs)
+    xb = math.ceil((2**31 - 1 if wl.max_budget is None else wl.max_budget) / bs)
+    g = wl.group_size
+    out = {"meta": json.dumps(dict(name=name, workload=wl.__dict__, lookup=lookup))}
+
+    for layer in range(wl.num_layers):
+        q, k, v = make_qkv(wl, layer, dtype=torch.bfloat16)
+        out[f"L{layer}_digest"] = np.frombuffer(bytes.fromhex(tensor_digest(q, k, v)), dtype=np.uint8)
+        rec = {"jsd": [], "cover_idx": [], "sumpool": []}
+
+        real = {n: getattr(att, n) for n in
+                ("square_root_js_divergence", "score_cover_idx", "torch_bhn_sumpool")}
+
+        def jsd(p, qq):
+            rec["jsd"].append((p.detach().clone(), qq.detach().clone()))
+            return real["square_root_js_divergence"](p, qq)
+
+        def cover_idx(x, score, padding_value=0):
+            rec["cover_idx"].append(x.detach().clone())
+            return real["score_cover_idx"](x, score, padding_value)
+
+        def sumpool(x, ks):
+            rec["sumpool"].append(x.detach().clone())
+            return real["torch_bhn_sumpool"](x, ks)
+
+        def pool(x, ks, pool_type="avg"):
+            return orc.block_mean_pool(x[0], ks)[None]
+
+        att.square_root_js_divergence = jsd
+        att.score_cover_idx = cover_idx
+        att.torch_bhn_sumpool = sumpool
+        att.triton_bnhd_pool = pool
+        try:
+            with cuda_string_to_cpu():
+                k_rep = k.repeat_interleave(g, dim=1)
+                block_idx, use_dense = ref_state.get_active_blocks(
+                    q[None].contiguous(), k_rep[None].contiguous(), layer, wl.num_q_heads, bs, mb, xb,
+                    wl.pattern_threshold, wl.similarity_threshold, wl.fallback_threshold,
+                    wl.queryaware_threshold, False)
+        finally:
+            for n, f in real.items():
+                setattr(att, n, f)
+
+        sets = [block_idx[0][h].to(torch.int64) for h in range(wl.num_q_heads)]
+        use_dense = use_dense[0]
+        vertical, slash = rec["sumpool"][0][0], rec["sumpool"][1][0]     # [H,N] fp32, un-pooled
+        avg_qk = rec["jsd"][0][0][0]                                       # [H,nb]
+        use_qa = real["square_root_js_divergence"](rec["jsd"][0][0], rec["jsd"][0][1])[0] < wl.queryaware_threshold
+        qa_heads = torch.nonzero(use_qa).flatten().tolist()
+        assert len(qa_heads) == len(rec["cover_idx"])
+
+        o, avg = orc.sparse_attention(q, k, v, sets, use_dense, bs)
+        avg_full = torch.zeros(1, wl.num_q_heads, nb, nb)
+        for h, a in avg.items():
+            avg_full[0, h] = a
+        with cuda_string_to_cpu():
+            ref_state.update_pivotal_attns(layer, avg_full, use_dense[None], wl.pattern_threshold)
+
+        pre = f"L{layer}_"
+        out[pre + "set_len"] = np.array([len(s) for s in sets], dtype=np.int64)
+        out[pre + "set_cat"] = torch.cat(sets).numpy()
+        out[pre + "use_dense"] = use_dense.numpy()
+        out[pre + "use_qa"] = use_qa.numpy()
+        out[pre + "vertical"] = vertical.numpy()
+        out[pre + "slash"] = slash.numpy()
+        out[pre + "avg_qk"] = avg_qk.numpy()
+        out[pre + "qa_heads"] = np.array(qa_heads, dtype=np.int64)
+        if qa_heads:
+            out[pre + "qa_scores"] = torch.stack(rec["cover_idx"]).numpy()
+        out[pre + "dense_heads"] = np.array(sorted(avg.keys()), dtype=np.int64)
+        if avg:
+            out[pre + "avg_attn"] = torch.stack([avg[h] for h in sorted(avg.keys())]).numpy()
+        print(f"{name} L{layer}: dense={torch.nonzero(use_dense).flatten().tolist()} qa={qa_heads} "
+              f"density={[round(len(s) / (nb * (nb + 1) / 2), 3) for s in sets]}")
+
+    # state at the end of the forward
+    for cid in lookup["shared_clusters"]:
+        ph = ref_state.pivotal_heads[cid][0]
+        out[f"S{cid}_pivot_head"] = np.array(-1 if ph is None else int(ph), dtype=np.int64)
+        pat = ref_state.pivotal_patterns[cid][0]
+        if pat is not None:
+            out[f"S{cid}_pattern"] = pat.numpy()
+        r = ref_state.pivotal_vs_ratio[cid][0]
+        out[f"S{cid}_vs_ratio"] = np.array(float("nan") if r is None else r, dtype=np.float64)
+    np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **out)
+
+
+def helper_vectors(utils):
+    """Known-answer vectors for the look-alike cover rules and the other helpers."""
+    g = torch.Generator().manual_seed(7)
+    out = {}
+    x = torch.rand(6, 333, generator=g)
+    x = x ** 4
+    x = x / x.sum(-1, keepdim=True)
+    out["cover_x"] = x.numpy()
+    for thr in (0.5, 0.9, 0.95):
+        out[f"cover_topk_{thr}"] = utils.score_cover_topk(x, thr).numpy()
+        out[f"cover_rows_{thr}"] = utils.score_cover_idx_each_row(x, thr).numpy()
+        out[f"cover_global_{thr}"] = utils.score_cover_idx(x.reshape(-1), thr * 6).numpy()
+    p = torch.rand(5, 40, generator=g); p /= p.sum(-1, keepdim=True)
+    q = torch.rand(5, 40, generator=g); q /= q.sum(-1, keepdim=True)
+    q[4, 3] = 0.0
+    out["jsd_p"], out["jsd_q"] = p.numpy(), q.numpy()
+    out["jsd"] = utils.square_root_js_divergence(p, q).numpy()
+    m = torch.rand(1, 3, 16, 100, generator=g)
+    out["diag_in"] = m.numpy()
+    out["diag_out"] = utils.sum_all_diagonal_matrix(m).numpy()
+    out["sumpool_out"] = utils.torch_bhn_sumpool(m[0], 16).numpy()
+    v = torch.tensor([[[0, 3, 5]]]); s = torch.tensor([[[0, 2]]])
+    out["vs_v"], out["vs_s"] = v.numpy(), s.numpy()
+    out["vs_out"] = utils.combine_vertical_slash_indices(v, s, 7).numpy()
+    np.savez_compressed(os.path.join(HERE, "helpers.npz"), **out)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default=None)
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    import importlib
+    att = importlib.import_module("shareprefill.attn.attention_sharing")
+    utils = importlib.import_module("shareprefill.attn.utils")
+    torch.manual_seed(0)
+    helper_vectors(utils)
+    for name, spec in CASES.items():
+        if args.only and name != args.only:
+            continue
+        run_case(name, spec, att)
+
+
+if __name__ == "__main__":
+    main()

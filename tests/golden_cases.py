@@ -1,0 +1,71 @@
+"""Loader for the golden vectors under tests/golden (made by make_golden.py)."""
+import hashlib
+import json
+import math
+import os
+
+import numpy as np
+import torch
+
+from shareprefill_b200.workloads import AttentionWorkload, make_qkv
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+CASE_NAMES = ["peaky_share", "peaky_default", "diffuse_qa", "ragged_rope"]
+
+
+class GoldenCase:
+    def __init__(self, name):
+        self.name = name
+        self.z = np.load(os.path.join(GOLDEN_DIR, f"{name}.npz"))
+        meta = json.loads(str(self.z["meta"]))
+        self.wl = AttentionWorkload(**meta["workload"])
+        self.lookup = meta["lookup"]
+        self.bs = self.wl.block_size
+        self.nb = self.wl.num_blocks
+        self.min_blocks = math.ceil(self.wl.min_budget / self.bs)
+        mx = 2**31 - 1 if self.wl.max_budget is None else self.wl.max_budget
+        self.max_blocks = math.ceil(mx / self.bs)
+
+    def knobs(self):
+        wl = self.wl
+        return dict(block_size=wl.block_size, min_blocks=self.min_blocks, max_blocks=self.max_blocks,
+                    pattern_threshold=wl.pattern_threshold, similarity_threshold=wl.similarity_threshold,
+                    fallback_threshold=wl.fallback_threshold, queryaware_threshold=wl.queryaware_threshold)
+
+    def t(self, key):
+        return torch.from_numpy(self.z[key])
+
+    def has(self, key):
+        return key in self.z.files
+
+    def sets(self, layer):
+        lens = self.z[f"L{layer}_set_len"].tolist()
+        cat = self.t(f"L{layer}_set_cat")
+        out, o = [], 0
+        for n in lens:
+            out.append(cat[o:o + n])
+            o += n
+        return out
+
+    def qkv(self, layer):
+        q, k, v = make_qkv(self.wl, layer, dtype=torch.bfloat16)
+        hsh = hashlib.sha256()
+        for t in (q, k, v):
+            hsh.update(t.contiguous().view(torch.uint8).numpy().tobytes())
+        want = bytes(self.z[f"L{layer}_digest"].tolist()).hex()
+        assert hsh.hexdigest() == want, "seeded generator no longer reproduces the golden inputs"
+        return q, k, v
+
+    def qa_scores(self, layer):
+        heads = self.z[f"L{layer}_qa_heads"].tolist()
+        if not heads:
+            return {}
+        sc = self.t(f"L{layer}_qa_scores")
+        return {h: sc[i] for i, h in enumerate(heads)}
+
+    def avg_attn(self, layer):
+        heads = self.z[f"L{layer}_dense_heads"].tolist()
+        if not heads:
+            return {}
+        a = self.t(f"L{layer}_avg_attn")
+        return {h: a[i] for i, h in enumerate(heads)}
