@@ -1,0 +1,228 @@
+// Last-block profile: softmax of the last `block_size` queries of every head against all
+// keys, reduced to the vertical profile (mean over the queries) and the slash profile (mean
+// over the queries along each anti-diagonal).  Restates attn/attention_sharing.py:127-167 and
+// sum_all_diagonal_matrix (attn/utils.py:79-86) as a streaming two-pass computation that never
+// materialises the [H, block, N] score tensor:
+//   pass 1  per (key tile, head): logits on mma.sync, per-row tile max and sum of exp
+//   reduce  per head: global row max M_i and normaliser Z_i
+//   pass 2  per (key tile, head): recompute logits, p = exp(l - M_i) / Z_i into shared memory,
+//           column sums -> vertical, anti-diagonal sums -> slash
+// Rounding points follow the reference's bf16 path: q / sqrt(D) is rounded to bf16, logits are
+// rounded to bf16 (its einsum output dtype) and the softmax runs in fp32.
+// Each slash element receives at most two addends (from two adjacent key tiles) on a zeroed
+// buffer, so the atomic adds are order independent.
+#include "spf_internal.cuh"
+#include "spf_mma.cuh"
+
+namespace spf {
+
+constexpr int EST_ROWS = 128;   // query rows per tile (block_size <= 128, padded)
+constexpr int EST_COLS = 128;   // keys per tile
+constexpr int EST_NT = 256;
+
+
+// Stage bf16(q / sqrt(D)) for the last rq queries of head h (rows >= rq are zero) in shared
+// memory and pull this warp's 16 rows into A fragments.  The staging area may be reused after
+// the trailing barrier.
+template <int D>
+__device__ __forceinline__ void est_load_q(const EstParams& p, int h, uint32_t sq,
+                                           uint32_t (&qf)[D / 16][4]) {
+  constexpr int CHUNKS = D / 8;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q0 = p.n_tokens - p.rq;
+  unsigned char* sq_ptr = reinterpret_cast<unsigned char*>(__cvta_shared_to_generic(sq));
+  for (int i = tid; i < EST_ROWS * CHUNKS; i += EST_NT) {
+    const int row = i / CHUNKS, ch = i % CHUNKS;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (row < p.rq) {
+      val = *reinterpret_cast<const uint4*>(p.q + int64_t(q0 + row) * p.q_sn + int64_t(h) * p.q_sh + ch * 8);
+      __nv_bfloat162* pr = reinterpret_cast<__nv_bfloat162*>(&val);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 f = __bfloat1622float2(pr[e]);
+        pr[e] = __floats2bfloat162_rn(f.x / p.sqrt_d, f.y / p.sqrt_d);
+      }
+    }
+    *reinterpret_cast<uint4*>(sq_ptr + tile_off<D>(row, ch)) = val;
+  }
+  __syncthreads();
+  const int qrow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) ldmatrix_x4(qf[ks], sq + tile_off<D>(qrow, ks * 2 + (lane >> 4)));
+  __syncthreads();
+}
+
+// Load key tile `tile` of the head's KV head into shared memory at sk and compute
+// S = Q K^T rounded to bf16 with the causal mask.  Ends with all warps past their reads of sk.
+template <int D>
+__device__ __forceinline__ void est_tile_scores(const EstParams& p, int h, int tile, uint32_t sk,
+                                                const uint32_t (&qf)[D / 16][4],
+                                                float (&s)[EST_COLS / 8][4]) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kvh = h / p.group;
+  const int c0 = tile * EST_COLS;
+  const int q0 = p.n_tokens - p.rq;
+  load_tile_async<EST_COLS, D, EST_NT>(sk, p.k + int64_t(kvh) * p.k_sh + int64_t(c0) * p.k_sn, p.k_sn,
+                                       min(EST_COLS, p.n_tokens - c0), tid);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < EST_COLS / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+    for (int jp = 0; jp < EST_COLS / 16; ++jp) {
+      uint32_t bf[4];
+      const int krow = jp * 16 + (lane & 7) + (lane >> 4) * 8;
+      ldmatrix_x4(bf, sk + tile_off<D>(krow, ks * 2 + ((lane >> 3) & 1)));
+      mma_bf16_16816(s[2 * jp], qf[ks], bf[0], bf[1]);
+      mma_bf16_16816(s[2 * jp + 1], qf[ks], bf[2], bf[3]);
+    }
+  }
+  __syncthreads();
+  const int row_lo = warp * 16 + (lane >> 2);
+#pragma unroll
+  for (int j = 0; j < EST_COLS / 8; ++j) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int kpos = c0 + j * 8 + (lane & 3) * 2 + (e & 1);
+      const int qpos = q0 + row_lo + (e >> 1) * 8;
+      s[j][e] = (kpos > qpos) ? -INFINITY : bf16_round(s[j][e]);
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(EST_NT) lastblock_stats_kernel(const EstParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const int h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t qf[D / 16][4];
+  est_load_q<D>(p, h, sbase, qf);
+  const int t_end = min(p.ntiles, (int(blockIdx.x) + 1) * p.tiles_per_cta);
+  for (int tile = blockIdx.x * p.tiles_per_cta; tile < t_end; ++tile) {
+    float s[EST_COLS / 8][4];
+    est_tile_scores<D>(p, h, tile, sbase, qf, s);
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < EST_COLS / 8; ++j) {
+      mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+      mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+    }
+    const float m0 = (mx[0] == -INFINITY) ? 0.f : mx[0];
+    const float m1 = (mx[1] == -INFINITY) ? 0.f : mx[1];
+#pragma unroll
+    for (int j = 0; j < EST_COLS / 8; ++j) {
+      sum[0] += expf(s[j][0] - m0) + expf(s[j][1] - m0);
+      sum[1] += expf(s[j][2] - m1) + expf(s[j][3] - m1);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+    }
+    if ((lane & 3) == 0) {
+      const int row = warp * 16 + (lane >> 2);
+      const int64_t base = (int64_t(h) * p.ntiles + tile) * EST_ROWS;
+      p.part_m[base + row] = mx[0];
+      p.part_l[base + row] = sum[0];
+      p.part_m[base + row + 8] = mx[1];
+      p.part_l[base + row + 8] = sum[1];
+    }
+  }
+}
+
+__global__ void lastblock_reduce_kernel(const EstParams p) {
+  const int h = blockIdx.x, row = threadIdx.x;  // 128 threads
+  const float* pm = p.part_m + int64_t(h) * p.ntiles * EST_ROWS + row;
+  const float* pl = p.part_l + int64_t(h) * p.ntiles * EST_ROWS + row;
+  float m = -INFINITY;
+  for (int t = 0; t < p.ntiles; ++t) m = fmaxf(m, pm[int64_t(t) * EST_ROWS]);
+  double z = 0.0;
+  for (int t = 0; t < p.ntiles; ++t) {
+    const float mt = pm[int64_t(t) * EST_ROWS];
+    if (mt != -INFINITY) z += static_cast<double>(pl[int64_t(t) * EST_ROWS]) * static_cast<double>(expf(mt - m));
+  }
+  p.row_m[h * EST_ROWS + row] = m;
+  p.row_z[h * EST_ROWS + row] = static_cast<float>(z);
+}
+
+template <int D>
+__global__ void __launch_bounds__(EST_NT) lastblock_profile_kernel(const EstParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int LD = EST_COLS + 1;
+  constexpr int P_BYTES = ((EST_ROWS * LD * 4 + 127) / 128) * 128;
+  float* P = reinterpret_cast<float*>(smem);            // [128][129] fp32
+  const uint32_t sk = smem_u32(smem) + P_BYTES;         // K tile (also stages Q once)
+  const int h = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint32_t qf[D / 16][4];
+  est_load_q<D>(p, h, sk, qf);
+  const int row_lo = warp * 16 + (lane >> 2);
+  const float M0 = p.row_m[h * EST_ROWS + row_lo], M1 = p.row_m[h * EST_ROWS + row_lo + 8];
+  const float Z0 = p.row_z[h * EST_ROWS + row_lo], Z1 = p.row_z[h * EST_ROWS + row_lo + 8];
+  const int rq = p.rq;
+  const float inv_rows = 1.0f / static_cast<float>(rq);
+  const int t_end = min(p.ntiles, (int(blockIdx.x) + 1) * p.tiles_per_cta);
+  for (int tile = blockIdx.x * p.tiles_per_cta; tile < t_end; ++tile) {
+    float s[EST_COLS / 8][4];
+    est_tile_scores<D>(p, h, tile, sk, qf, s);
+#pragma unroll
+    for (int j = 0; j < EST_COLS / 8; ++j) {
+      const int c = j * 8 + (lane & 3) * 2;
+      P[row_lo * LD + c] = expf(s[j][0] - M0) / Z0;
+      P[row_lo * LD + c + 1] = expf(s[j][1] - M0) / Z0;
+      P[(row_lo + 8) * LD + c] = expf(s[j][2] - M1) / Z1;
+      P[(row_lo + 8) * LD + c + 1] = expf(s[j][3] - M1) / Z1;
+    }
+    __syncthreads();
+    const int c0 = tile * EST_COLS;
+    if (tid < EST_COLS && c0 + tid < p.n_tokens) {
+      float acc = 0.f;
+      for (int i = 0; i < rq; ++i) acc += P[i * LD + tid];
+      p.vertical[int64_t(h) * p.n_tokens + c0 + tid] = acc * inv_rows;
+    }
+    // anti-diagonals: element (i, jj) lands on tile-local index t = jj + (rq-1) - i
+    for (int t = tid; t < EST_COLS + rq - 1; t += EST_NT) {
+      const int i_lo = max(0, rq - 1 - t);
+      const int i_hi = min(rq - 1, EST_COLS - 1 + rq - 1 - t);
+      float acc = 0.f;
+      for (int i = i_lo; i <= i_hi; ++i) acc += P[i * LD + (t - (rq - 1) + i)];
+      const int n = c0 + t;
+      if (n < p.n_tokens) atomicAdd(&p.slash[int64_t(h) * p.n_tokens + n], acc * inv_rows);
+    }
+    __syncthreads();
+  }
+}
+
+template <int D>
+static int launch_estimate(const EstParams& p, cudaStream_t st) {
+  const dim3 grid(ceil_div(p.ntiles, p.tiles_per_cta), p.n_q_heads);
+  constexpr int TILE = EST_ROWS * D * 2;
+  constexpr int P_BYTES = ((EST_ROWS * (EST_COLS + 1) * 4 + 127) / 128) * 128;
+  cudaError_t e;
+  e = cudaFuncSetAttribute(lastblock_profile_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_BYTES + TILE);
+  if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
+  lastblock_stats_kernel<D><<<grid, EST_NT, TILE, st>>>(p);
+  lastblock_reduce_kernel<<<p.n_q_heads, EST_ROWS, 0, st>>>(p);
+  lastblock_profile_kernel<D><<<grid, EST_NT, P_BYTES + TILE, st>>>(p);
+  return check_launch();
+}
+
+int lastblock_profile(const EstParams& p, int head_dim, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(p.slash, 0, sizeof(float) * int64_t(p.n_q_heads) * p.n_tokens, st);
+  if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
+  if (head_dim == 128) return launch_estimate<128>(p, st);
+  if (head_dim == 64) return launch_estimate<64>(p, st);
+  return SPF_ERR_SHAPE;
+}
+
+}  // namespace spf
