@@ -36,6 +36,7 @@ def sparse_prefill_attention(sharing, q, k, v, layer_idx: int, num_heads: int, c
         config.queryaware_threshold, False)
     out = native.sparse_attention(q, k, v, pat.bitmap, block_size, scale, pat.flags, pat.slot_of_head,
                                   sharing.state)
+    sharing._mark("attention")
     sharing.update_pivotal_attns(layer_idx, None, use_dense, config.pattern_threshold)
     return out, pat
 

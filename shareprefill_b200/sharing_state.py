@@ -75,6 +75,11 @@ class AttentionSharing:
         self._state: Optional[native.SharingStateBuffer] = None
         self._needs_reset = True
         self.last_pattern: Optional[BlockPattern] = None
+        self.on_stage = None   # optional callable(stage_name), e.g. to record CUDA events
+
+    def _mark(self, stage: str):
+        if self.on_stage is not None:
+            self.on_stage(stage)
 
     # ---- lookup
     @staticmethod
@@ -165,10 +170,12 @@ class AttentionSharing:
         si = stage_inputs or {}
 
         avg_q, avg_k = native.pool_qk(q, k, block_size)
+        self._mark("pool")
         if "vertical" in si:
             vertical, slash = si["vertical"], si["slash"]
         else:
             vertical, slash = native.lastblock_profile(q, k, block_size)
+        self._mark("profile")
         max_blocks = min(int(max_budget), nb)
         nv, ns, vpool, spool = native.profile_budgets(vertical, slash, block_size, pattern_threshold,
                                                       min_budget, max_blocks)
@@ -189,6 +196,7 @@ class AttentionSharing:
                                      avg_qk=avg_qk, avg_k=avg_k, avg_q=avg_q, jsd_qa=jsd_qa,
                                      jsd_v=jsd_v, jsd_s=jsd_s))
         self.last_pattern = pat
+        self._mark("select")
         return pat, pat.use_dense
 
     def update_pivotal_attns(self, layer_idx, avg_attn, use_dense, pattern_threshold=0.9):
@@ -197,8 +205,8 @@ class AttentionSharing:
         state by the attention kernel; ``avg_attn`` / ``use_dense`` are accepted for signature
         compatibility and ignored."""
         pat = self.last_pattern
-        if pat is None or self._state is None or not self.slot_ids:
-            return
-        native.update_pivots(pat.flags, pat.slot_of_head, self._state, pattern_threshold)
-        if self.exchange is not None:
-            self.exchange.share_new_pivots(self, layer_idx)
+        if pat is not None and self._state is not None and self.slot_ids:
+            native.update_pivots(pat.flags, pat.slot_of_head, self._state, pattern_threshold)
+            if self.exchange is not None:
+                self.exchange.share_new_pivots(self, layer_idx)
+        self._mark("pivot_update")
