@@ -83,6 +83,34 @@ int spf_lastblock_profile(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                           int block_size, float* vertical, float* slash,
                           void* scratch, int64_t scratch_bytes, void* stream);
 
+/* spf_lastblock_profile_static: the same computation for callers that cannot allocate
+ * device memory.  (No counterpart in the reference; added for such callers.)
+ *
+ * Who needs it: code that runs where cudaMalloc / a framework allocator is off limits, e.g. a
+ * plugin living inside another runtime's fixed memory plan that is handed only its input and
+ * output buffers, or a serving loop whose memory pool is frozen after warm-up.  They pass
+ * inputs and outputs only; the pass-1 scratch is a fixed array inside the library.
+ *
+ * Limits and rules:
+ *   - The array is SPF_STATIC_SCRATCH_BYTES (8 MiB + 128 KiB) and is resident on every GPU
+ *     that loads the library until the process exits.  A call whose scratch need (the value
+ *     spf_lastblock_scratch_bytes reports) exceeds it returns SPF_ERR_TOO_LARGE.  The array
+ *     covers n_q_heads * (ceil(n_tokens/128) + 1) <= 8320, e.g. 32 heads x 32K tokens or
+ *     8 heads x 128K tokens.
+ *   - The first call on a device looks up the array's device address (that device must be
+ *     current); make that first call outside any stream capture.
+ *   - The function calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - All calls on a device share the one array: calls that may overlap on the GPU (different
+ *     streams, threads or processes sharing a context) race; serialise them.  Nothing in the
+ *     array needs to start at zero - every word is written before it is read - and the
+ *     previous call's contents are simply overwritten.
+ */
+#define SPF_STATIC_SCRATCH_BYTES (8 * 1024 * 1024 + 128 * 1024)
+int spf_lastblock_profile_static(const void* q, int64_t q_stride_n, int64_t q_stride_h,
+                                 const void* k, int64_t k_stride_n, int64_t k_stride_h,
+                                 int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
+                                 int block_size, float* vertical, float* slash, void* stream);
+
 /* ---------------------------------------------------------------- budgets + pooled profiles
  * Per head: number of vertical / slash blocks from the cumulative-mass rule
  * (score_cover_topk, attn/utils.py:47-50; attn/attention_sharing.py:169-176) and the

@@ -226,3 +226,83 @@ int lastblock_profile(const EstParams& p, int head_dim, cudaStream_t st) {
 }
 
 }  // namespace spf
+
+// ------------------------------------------------------------------------------------------
+// Entry point for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc (or torch's allocator) at the point where
+// the profile is needed: a plugin running inside another framework's memory plan that hands it
+// only the input and output buffers, or a serving loop whose allocator is frozen once warm-up
+// ends.  For them the pass-1 scratch lives in the fixed array below instead of a caller buffer.
+// The array is part of the library image: every GPU that loads the library holds
+// SPF_STATIC_SCRATCH_BYTES of it until the process exits.
+//
+// In host code `g_static_scratch` is only a stand-in for the symbol, not a device address: the
+// address each device uses is looked up with cudaGetSymbolAddress while that device is current,
+// once per device, and that pointer is what the kernels receive.
+#include <mutex>
+
+namespace spf {
+constexpr int64_t STATIC_SCRATCH_BYTES = SPF_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+static void* g_scratch_addr[MAX_DEVICES] = {nullptr};
+static std::mutex g_scratch_mutex;
+
+// Device address of the static scratch on the current device (looked up on first use).
+static int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
+  if (dev < 0 || dev >= MAX_DEVICES) return SPF_ERR_RANGE;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      note_cuda_error(e);
+      return SPF_ERR_LAUNCH;
+    }
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return SPF_OK;
+}
+}  // namespace spf
+
+extern "C" int spf_lastblock_profile_static(const void* q, int64_t q_stride_n, int64_t q_stride_h,
+                                            const void* k, int64_t k_stride_n, int64_t k_stride_h,
+                                            int n_tokens, int n_q_heads, int n_kv_heads, int head_dim,
+                                            int block_size, float* vertical, float* slash, void* stream) {
+  using namespace spf;
+  if (!q || !k || !vertical || !slash) return SPF_ERR_NULL;
+  if (!supported_head_dim(head_dim) || !supported_block_size(block_size)) return SPF_ERR_SHAPE;
+  if (n_tokens < block_size || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return SPF_ERR_SHAPE;
+  if (n_q_heads > SPF_MAX_HEADS || ceil_div(n_tokens, block_size) > SPF_MAX_BLOCKS) return SPF_ERR_TOO_LARGE;
+  if ((q_stride_n | q_stride_h | k_stride_n | k_stride_h) % 8 != 0 || !aligned16(q) || !aligned16(k))
+    return SPF_ERR_ALIGN;
+  // same scratch layout as spf_lastblock_profile: two [H][tiles][128] and two [H][128] fp32 arrays
+  const int ntiles = ceil_div(n_tokens, EST_COLS);
+  const int64_t part = align256(int64_t(n_q_heads) * ntiles * EST_ROWS * 4);
+  const int64_t rows = align256(int64_t(n_q_heads) * EST_ROWS * 4);
+  if (2 * part + 2 * rows > STATIC_SCRATCH_BYTES) return SPF_ERR_TOO_LARGE;  // heads x tokens too big for the fixed scratch
+  void* base = nullptr;
+  const int rc = static_scratch_for_current_device(&base);
+  if (rc != SPF_OK) return rc;
+  EstParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q); p.q_sn = q_stride_n; p.q_sh = q_stride_h;
+  p.k = static_cast<const __nv_bfloat16*>(k); p.k_sn = k_stride_n; p.k_sh = k_stride_h;
+  p.n_tokens = n_tokens; p.n_q_heads = n_q_heads; p.group = n_q_heads / n_kv_heads;
+  p.rq = block_size; p.ntiles = ntiles;
+  const int tpc = (ntiles * n_q_heads) / (148 * 8);
+  p.tiles_per_cta = tpc < 1 ? 1 : (tpc > 8 ? 8 : tpc);
+  p.sqrt_d = sqrtf(static_cast<float>(head_dim));
+  char* s = static_cast<char*>(base);
+  p.part_m = reinterpret_cast<float*>(s);
+  p.part_l = reinterpret_cast<float*>(s + part);
+  p.row_m = reinterpret_cast<float*>(s + 2 * part);
+  p.row_z = reinterpret_cast<float*>(s + 2 * part + rows);
+  p.vertical = vertical; p.slash = slash;
+  return lastblock_profile(p, head_dim, static_cast<cudaStream_t>(stream));
+}

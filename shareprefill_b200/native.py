@@ -31,6 +31,7 @@ SIGNATURES = {
     "spf_pool_qk": (_I, [_P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _I, _P, _P, _P]),
     "spf_lastblock_scratch_bytes": (_L, [_I, _I, _I]),
     "spf_lastblock_profile": (_I, [_P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _I, _P, _P, _P, _L, _P]),
+    "spf_lastblock_profile_static": (_I, [_P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _I, _P, _P, _P]),
     "spf_profile_budgets": (_I, [_P, _P, _I, _I, _I, _D, _I, _I, _P, _P, _P, _P, _P]),
     "spf_pooled_last_row": (_I, [_P, _L, _L, _P, _I, _I, _I, _I, _I, _P, _P]),
     "spf_sharing_state_bytes": (_L, [_I, _I]),
