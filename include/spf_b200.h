@@ -217,6 +217,11 @@ int spf_sparse_attention(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                          const int32_t* head_flags, const int32_t* slot_of_head, void* state,
                          int n_slots, void* out, void* stream);
 
+/* Number of bounded device-side waits that gave up since the library was loaded (0 in a
+ * healthy run).  The tcgen05 kernel never spins without a limit: a wait that runs out makes
+ * its CTA drain and return, and is counted here.  Synchronises the device. */
+int spf_device_timeouts(void);
+
 /* ---------------------------------------------------------------- pivot update
  * For every head elected pivot in this layer: per-row cumulative-mass cover of its
  * block-mass matrix, crossing element included (score_cover_idx_each_row,

@@ -1,5 +1,6 @@
 // C ABI of libspf_b200.so: argument validation and dispatch.  See include/spf_b200.h.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "spf_internal.cuh"
@@ -257,8 +258,25 @@ int spf_sparse_attention(const void* q, int64_t q_stride_n, int64_t q_stride_h, 
   p.n_tokens = n_tokens; p.n_q_heads = n_q_heads; p.group = n_q_heads / n_kv_heads;
   p.nb = ceil_div(n_tokens, block_size); p.nbw = (p.nb + 31) / 32;
   p.scale_log2 = static_cast<float>(softmax_scale * 1.4426950408889634);
-  return sparse_attention_generic(p, block_size, head_dim, static_cast<cudaStream_t>(stream));
+  p.pivot_only = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // block_size = head_dim = 128 runs on the tcgen05 kernel; SPF_ATTENTION_KERNEL=generic (a test
+  // hook) keeps the mma.sync kernel, which also serves every other supported shape
+  const char* force = std::getenv("SPF_ATTENTION_KERNEL");
+  const bool want_tc5 = block_size == 128 && head_dim == 128 && !(force && std::strcmp(force, "generic") == 0);
+  if (want_tc5) {
+    rc = sparse_attention_tc5(p, n_kv_heads, st);
+    if (rc == SPF_OK) {
+      if (!with_state) return SPF_OK;
+      p.pivot_only = 1;   // pivot heads: the block-mass matrix comes from the two-sweep kernel
+      return sparse_attention_generic(p, block_size, head_dim, st);
+    }
+    if (rc != SPF_ERR_SHAPE) return rc;
+  }
+  return sparse_attention_generic(p, block_size, head_dim, st);
 }
+
+int spf_device_timeouts(void) { return static_cast<int>(tc5_timeout_count()); }
 
 int spf_update_pivots(const int32_t* head_flags, const int32_t* slot_of_head, void* state, int n_slots, int n_heads,
                       int nb, double pattern_threshold, void* stream) {

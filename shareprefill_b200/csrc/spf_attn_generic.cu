@@ -63,6 +63,9 @@ __global__ void __launch_bounds__(BS * 2) sparse_attn_generic_kernel(const AttnP
   // heavy (late) query blocks first
   const int r = p.nb - 1 - static_cast<int>(blockIdx.x / p.n_q_heads);
   const int h = static_cast<int>(blockIdx.x % p.n_q_heads);
+  const bool is_pivot = p.head_flags != nullptr && p.pivot_attn != nullptr &&
+                        (p.head_flags[h] & SPF_HEAD_PIVOT) && p.slot_of_head[h] >= 0;
+  if (p.pivot_only && !is_pivot) return;
   const int kvh = h / p.group;
   const int row0 = r * BS;
   const int rows_valid = min(BS, p.n_tokens - row0);
@@ -218,7 +221,7 @@ __global__ void __launch_bounds__(BS * 2) sparse_attn_generic_kernel(const AttnP
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int tok = qpos0 + i * 8;
-    if (tok < p.n_tokens) {
+    if (tok < p.n_tokens && !p.pivot_only) {
       __nv_bfloat16* orow = p.out + (int64_t(tok) * p.n_q_heads + h) * D + (lane & 3) * 2;
 #pragma unroll
       for (int t = 0; t < NTILES_O; ++t) {
@@ -229,9 +232,8 @@ __global__ void __launch_bounds__(BS * 2) sparse_attn_generic_kernel(const AttnP
   }
 
   // ---- pivot heads: block mass matrix
-  if (p.head_flags == nullptr || !(p.head_flags[h] & SPF_HEAD_PIVOT) || p.pivot_attn == nullptr) return;
+  if (!is_pivot) return;
   const int slot = p.slot_of_head[h];
-  if (slot < 0) return;
   float* arow = p.pivot_attn + (int64_t(slot) * p.nb + r) * p.nb;
   float lse[2];
 #pragma unroll

@@ -1,0 +1,535 @@
+// Block-sparse causal flash attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA)
+// for block_size = head_dim = 128.
+//
+// One CTA owns one query block row of up to TWO query heads of the same KV group, so every K/V
+// tile fetched by TMA serves both heads (GQA reuse); the two heads ping-pong on the tensor pipe.
+//
+//   warp 0      TMA producer: Q tiles once, then K and V tiles of the union of both heads' bitmap
+//               rows through a 2-stage ring (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   warp 1      MMA issuer: S_h = Q_h K^T (both operands in shared memory) and O_h += P_h V
+//               (P_h read from TMEM, V from shared memory) with tcgen05.mma, accumulators in TMEM;
+//               completion is signalled to mbarriers with tcgen05.commit
+//   warps 2-5   softmax warpgroup of head A: a thread owns one query row; tcgen05.ld of S, base-2
+//               online softmax with scale*log2(e) folded in, P rounded to bf16 and written back
+//               over S with tcgen05.st, O rescaled in TMEM only when the running maximum moved by
+//               more than 2^8 (exact: the final normalisation uses the same reference point)
+//   warps 6-9   the same for head B
+//
+// TMEM (512 columns): S_A/P_A [0,128)  S_B/P_B [128,256)  O_A [256,384)  O_B [384,512).
+// Arithmetic matches block_wise_prefill_attention_kernel (attn/shareprefill_attn.py:381-471):
+// fp32 scores, causal mask on the diagonal block, P -> bf16 before P V, fp32 accumulation, bf16
+// output.  Every mbarrier wait is bounded; on a timeout the CTA raises a shared abort flag, all
+// roles drain and the kernel returns after recording the event in a device-side counter.
+#include <cuda.h>
+
+#include "spf_internal.cuh"
+
+namespace spf {
+
+constexpr int TC_BS = 128;
+constexpr int TC_D = 128;
+constexpr int TC_THREADS = 320;
+constexpr int TC_STAGES = 2;
+constexpr uint32_t TC_TILE_BYTES = TC_BS * TC_D * 2;        // 32 KiB: one 128x128 bf16 tile
+constexpr uint32_t TC_SLAB_BYTES = TC_TILE_BYTES / 2;       // [128 rows][64 elements]
+constexpr uint32_t TC_SMEM_Q = 0;                           // 2 tiles
+constexpr uint32_t TC_SMEM_KV = 2 * TC_TILE_BYTES;          // per stage: K tile, V tile
+constexpr uint32_t TC_SMEM_BAR = TC_SMEM_KV + TC_STAGES * 2 * TC_TILE_BYTES;
+constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_BAR + 256;
+constexpr float TC_RESCALE_LOG2 = 8.0f;
+
+static __device__ unsigned int g_tc5_timeouts = 0;
+
+struct Tc5Params {
+  __nv_bfloat16* out;
+  const uint32_t* bitmap;
+  int n_tokens, n_q_heads, n_kv_heads, group, pairs, nb, nbw;
+  float scale_log2;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false once the CTA has aborted (unless `drain`) or after ~1 s without completion.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          bool drain = false) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  int spins = 0;
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if ((++spins & 63) == 0) {
+      if (*abort_flag && !drain) return false;
+      if (global_ns() - t0 > 1000000000ull) {
+        *abort_flag = 1;
+        atomicAdd(&g_tc5_timeouts, 1u);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+// D(tmem) (+)= A(smem desc) * B(smem desc)
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// D(tmem) (+)= A(tmem) * B(smem desc)
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  tc_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+// 16 packed bf16x2 words -> 16 consecutive columns
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return (static_cast<uint32_t>(__bfloat16_as_ushort(v.y)) << 16) | __bfloat16_as_ushort(v.x);
+}
+
+// shared-memory matrix descriptors, 128-byte swizzle, descriptor version 1
+// K-major operand ([rows][64 elements] slabs, 8-row groups 1024 bytes apart)
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  return (uint64_t((saddr >> 4) & 0x3fff)) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// MN-major operand (V: [keys][64 d] slabs; 8-key groups 1024 bytes apart, 64-d slabs 16 KiB apart)
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
+  return (uint64_t((saddr >> 4) & 0x3fff)) | (uint64_t(TC_SLAB_BYTES >> 4) << 16) | (uint64_t(1024 >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// instruction descriptor: bf16 x bf16 -> fp32, M = 128, N = 128
+constexpr uint32_t TC_IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(128 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+constexpr uint32_t TC_IDESC_PV = TC_IDESC_QK | (1u << 16);   // B (V) is MN-major
+
+// Walks the union of two bitmap rows in ascending column order; flags bit h = head h visits it.
+struct PairWalker {
+  const uint32_t* wa; const uint32_t* wb;
+  int row, nwords, w;
+  uint32_t ca, cb;
+  __device__ uint32_t lim(int wi, uint32_t x) const {
+    const int last = row - (wi << 5);
+    return last >= 31 ? x : (x & ((2u << last) - 1u));
+  }
+  __device__ void load(int wi) {
+    ca = wa ? lim(wi, __ldg(wa + wi)) : 0u;
+    cb = wb ? lim(wi, __ldg(wb + wi)) : 0u;
+  }
+  __device__ void init(const uint32_t* a, const uint32_t* b, int row_) {
+    wa = a; wb = b; row = row_; nwords = (row_ >> 5) + 1; w = 0;
+    load(0);
+  }
+  __device__ int next(int& flags) {
+    while ((ca | cb) == 0u) {
+      if (++w >= nwords) { flags = 0; return -1; }
+      load(w);
+    }
+    const int b = __ffs(ca | cb) - 1;
+    flags = int((ca >> b) & 1u) | (int((cb >> b) & 1u) << 1);
+    const uint32_t clr = ~(1u << b);
+    ca &= clr; cb &= clr;
+    return (w << 5) + b;
+  }
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const Tc5Params p) {
+  // once several waits have run out the kernel is not making progress: later CTAs do nothing
+  if (*reinterpret_cast<volatile unsigned int*>(&g_tc5_timeouts) > 16u) return;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // the swizzled tiles need 1024-byte alignment; the launch reserves 1 KiB of slack for it
+  unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+  const uint32_t sbase = smem_addr(smem);
+  // barriers
+  const uint32_t bar0 = sbase + TC_SMEM_BAR;
+  const uint32_t bar_q = bar0;
+  auto bar_kfull = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto bar_vfull = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto bar_kvempty = [&](int s) { return bar0 + 8u * (5 + s); };
+  auto bar_sfull = [&](int h) { return bar0 + 8u * (7 + h); };
+  auto bar_pready = [&](int h) { return bar0 + 8u * (9 + h); };
+  auto bar_odone = [&](int h) { return bar0 + 8u * (11 + h); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_SMEM_BAR + 8 * 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_SMEM_BAR + 8 * 13 + 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // heavy (late) query blocks first
+  int bid = blockIdx.x;
+  const int pair = bid % p.pairs; bid /= p.pairs;
+  const int kvh = bid % p.n_kv_heads; bid /= p.n_kv_heads;
+  const int r = p.nb - 1 - bid;
+  const int hA = kvh * p.group + pair * 2;
+  const bool hasB = (pair * 2 + 1) < p.group;
+  const int hB = hasB ? hA + 1 : -1;
+  const int row0 = r * TC_BS;
+  const uint32_t* rowA = p.bitmap + (int64_t(hA) * p.nb + r) * p.nbw;
+  const uint32_t* rowB = hasB ? p.bitmap + (int64_t(hB) * p.nb + r) * p.nbw : nullptr;
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < TC_STAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_vfull(s), 1); mbar_init(bar_kvempty(s), 1); }
+    for (int h = 0; h < 2; ++h) { mbar_init(bar_sfull(h), 1); mbar_init(bar_pready(h), 128); mbar_init(bar_odone(h), 1); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(bar_q, (hasB ? 2u : 1u) * TC_TILE_BYTES);
+      for (int h = 0; h < (hasB ? 2 : 1); ++h) {
+        const uint32_t dst = sbase + TC_SMEM_Q + h * TC_TILE_BYTES;
+        tma_load_3d(dst, &map_q, bar_q, 0, row0, hA + h);
+        tma_load_3d(dst + TC_SLAB_BYTES, &map_q, bar_q, 64, row0, hA + h);
+      }
+      PairWalker wk; wk.init(rowA, rowB, r);
+      int fl, i = 0, issued = 0;
+      for (int col = wk.next(fl); col >= 0; col = wk.next(fl), ++i) {
+        const int s = i & 1;
+        if (!mbar_wait(bar_kvempty(s), ((i >> 1) & 1) ^ 1, abort_flag)) break;
+        const uint32_t kdst = sbase + TC_SMEM_KV + s * 2 * TC_TILE_BYTES;
+        const uint32_t vdst = kdst + TC_TILE_BYTES;
+        mbar_expect_tx(bar_kfull(s), TC_TILE_BYTES);
+        tma_load_3d(kdst, &map_k, bar_kfull(s), 0, col * TC_BS, kvh);
+        tma_load_3d(kdst + TC_SLAB_BYTES, &map_k, bar_kfull(s), 64, col * TC_BS, kvh);
+        mbar_expect_tx(bar_vfull(s), TC_TILE_BYTES);
+        tma_load_3d(vdst, &map_v, bar_vfull(s), 0, col * TC_BS, kvh);
+        tma_load_3d(vdst + TC_SLAB_BYTES, &map_v, bar_vfull(s), 64, col * TC_BS, kvh);
+        issued = i + 1;
+      }
+      // drain: every copy this thread started must have landed before the CTA may exit
+      mbar_wait(bar_q, 0, abort_flag, true);
+      for (int j = (issued >= 2 ? issued - 2 : 0); j < issued; ++j) {
+        mbar_wait(bar_kfull(j & 1), (j >> 1) & 1, abort_flag, true);
+        mbar_wait(bar_vfull(j & 1), (j >> 1) & 1, abort_flag, true);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t tS[2] = {tmem + 0u, tmem + 128u};
+      const uint32_t tO[2] = {tmem + 256u, tmem + 384u};
+      auto issue_qk = [&](int h, int s) {
+        const uint32_t qa = sbase + TC_SMEM_Q + h * TC_TILE_BYTES;
+        const uint32_t ka = sbase + TC_SMEM_KV + s * 2 * TC_TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * TC_SLAB_BYTES + (ks & 3) * 32;
+          mma_ss(tS[h], desc_kmajor(qa + off), desc_kmajor(ka + off), TC_IDESC_QK, ks > 0);
+        }
+        tc_commit(bar_sfull(h));
+      };
+      auto issue_pv = [&](int h, int s, bool accumulate) {
+        const uint32_t va = sbase + TC_SMEM_KV + s * 2 * TC_TILE_BYTES + TC_TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ts(tO[h], tS[h] + ks * 8, desc_mnmajor(va + ks * 2048), TC_IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(bar_q, 0, abort_flag);
+      PairWalker wk; wk.init(rowA, rowB, r);
+      int fl, nfl;
+      int col = wk.next(fl);
+      int i = 0;
+      int nblk[2] = {0, 0};     // P tiles consumed per head
+      if (ok && col >= 0) {
+        ok = mbar_wait(bar_kfull(0), 0, abort_flag);
+        tc_fence_after();
+        if (ok) for (int h = 0; h < 2; ++h) if (fl & (1 << h)) issue_qk(h, 0);
+      }
+      while (ok && col >= 0) {
+        const int ncol = wk.next(nfl);
+        const int s = i & 1, ns = (i + 1) & 1;
+        bool v_ready = false, nk_ready = false;
+        const int last_h = (fl & 2) ? 1 : 0;
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (fl & (1 << h)) {
+            if (!v_ready) { ok = mbar_wait(bar_vfull(s), (i >> 1) & 1, abort_flag); v_ready = true; }
+            if (ok) ok = mbar_wait(bar_pready(h), nblk[h] & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(h, s, nblk[h] > 0);
+            ++nblk[h];
+            if (h == last_h) tc_commit(bar_kvempty(s));
+          }
+          if (ncol >= 0 && (nfl & (1 << h))) {
+            if (!nk_ready) { ok = mbar_wait(bar_kfull(ns), ((i + 1) >> 1) & 1, abort_flag); nk_ready = true; }
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(h, ns);
+          }
+        }
+        col = ncol; fl = nfl; ++i;
+      }
+      tc_commit(bar_odone(0));
+      tc_commit(bar_odone(1));
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warpgroups
+    const int h = (warp - 2) >> 2;                 // 0: head A, 1: head B
+    const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;           // query row within the block
+    const int head = h == 0 ? hA : hB;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const uint32_t tS = tmem + lane_base + uint32_t(h * 128);
+    const uint32_t tO = tmem + lane_base + uint32_t(256 + h * 128);
+    float m_used = -INFINITY, l_sum = 0.f;
+    int k = 0;
+    bool ok = head >= 0;
+    if (ok) {
+      PairWalker wk; wk.init(h == 0 ? rowA : rowB, nullptr, r);
+      int fl;
+      for (int col = wk.next(fl); col >= 0 && ok; col = wk.next(fl), ++k) {
+        ok = mbar_wait(bar_sfull(h), k & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const bool diag = (col == r);
+        // pass 1: row maximum of the raw scores
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float v[32];
+          tmem_ld32(tS + c * 32, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const bool masked = diag && (c * 32 + j > row);
+            mx = fmaxf(mx, masked ? -INFINITY : v[j]);
+          }
+        }
+        const float mb = mx * p.scale_log2;
+        float alpha = 1.f;
+        bool grow = false;
+        if (k == 0) {
+          m_used = mb;
+        } else if (mb > m_used + TC_RESCALE_LOG2) {
+          alpha = exp2f(m_used - mb);
+          m_used = mb;
+          l_sum *= alpha;
+          grow = true;
+        }
+        if (__any_sync(0xffffffffu, grow)) {
+          // S_h(k) is complete, hence so is every earlier P V of this head: O_h is stable
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            float v[32];
+            tmem_ld32(tO + c * 32, v);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= alpha;
+            tmem_st32(tO + c * 32, v);
+          }
+        }
+        // pass 2: P = 2^(s*scale - m) as bf16 over the first 64 columns of the S region
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float v[32];
+          tmem_ld32(tS + c * 32, v);
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const bool m0 = diag && (c * 32 + j > row), m1 = diag && (c * 32 + j + 1 > row);
+            const float p0 = m0 ? 0.f : fast_exp2(fmaf(v[j], p.scale_log2, -m_used));
+            const float p1 = m1 ? 0.f : fast_exp2(fmaf(v[j + 1], p.scale_log2, -m_used));
+            l_sum += p0 + p1;
+            pk[j >> 1] = pack2_bf16(p0, p1);
+          }
+          tmem_st16(tS + c * 16, pk);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_pready(h));
+      }
+      // ---- epilogue
+      const int tok = row0 + row;
+      __nv_bfloat16* orow = p.out + (int64_t(tok) * p.n_q_heads + head) * TC_D;
+      if (ok && k > 0) ok = mbar_wait(bar_odone(h), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        const float inv = (k > 0 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float v[32];
+          if (k > 0) {
+            tmem_ld32(tO + c * 32, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
+          if (tok < p.n_tokens) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o;
+              o.x = pack2_bf16(v[j] * inv, v[j + 1] * inv);
+              o.y = pack2_bf16(v[j + 2] * inv, v[j + 3] * inv);
+              o.z = pack2_bf16(v[j + 4] * inv, v[j + 5] * inv);
+              o.w = pack2_bf16(v[j + 6] * inv, v[j + 7] * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + j) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// [N][heads][128] bf16 view (strides in elements) as a 3-D tensor (d, token, head); box 64 x 128 x 1
+static bool make_map(CUtensorMap* m, const void* base, int n_tokens, int heads, int64_t sn, int64_t sh) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {cuuint64_t(TC_D), cuuint64_t(n_tokens), cuuint64_t(heads)};
+  const cuuint64_t strides[2] = {cuuint64_t(sn) * 2, cuuint64_t(sh) * 2};
+  const cuuint32_t box[3] = {64, TC_BS, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Returns SPF_ERR_SHAPE when the tensors cannot be described to TMA (the caller then uses the
+// generic kernel).
+int sparse_attention_tc5(const AttnParams& a, int n_kv_heads, cudaStream_t st) {
+  if (a.q_sn <= 0 || a.k_sn <= 0 || a.v_sn <= 0 || a.q_sh <= 0 || a.k_sh <= 0 || a.v_sh <= 0) return SPF_ERR_SHAPE;
+  CUtensorMap mq, mk, mv;
+  if (!make_map(&mq, a.q, a.n_tokens, a.n_q_heads, a.q_sn, a.q_sh) ||
+      !make_map(&mk, a.k, a.n_tokens, n_kv_heads, a.k_sn, a.k_sh) ||
+      !make_map(&mv, a.v, a.n_tokens, n_kv_heads, a.v_sn, a.v_sh))
+    return SPF_ERR_SHAPE;
+  Tc5Params p;
+  p.out = a.out; p.bitmap = a.bitmap; p.n_tokens = a.n_tokens; p.n_q_heads = a.n_q_heads;
+  p.n_kv_heads = n_kv_heads; p.group = a.group; p.pairs = (a.group + 1) / 2; p.nb = a.nb; p.nbw = a.nbw;
+  p.scale_log2 = a.scale_log2;
+  cudaError_t e = cudaFuncSetAttribute(sparse_attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(TC_SMEM_TOTAL + 1024));
+  if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
+  const unsigned grid = unsigned(a.nb) * unsigned(n_kv_heads) * unsigned(p.pairs);
+  sparse_attn_tc5_kernel<<<grid, TC_THREADS, TC_SMEM_TOTAL + 1024, st>>>(mq, mk, mv, p);
+  return check_launch();
+}
+
+unsigned int tc5_timeout_count() {
+  unsigned int v = 0;
+  cudaMemcpyFromSymbol(&v, g_tc5_timeouts, sizeof(v));
+  return v;
+}
+
+}  // namespace spf

@@ -16,6 +16,7 @@ struct AttnParams {
   float* pivot_attn;       // state.pivot_attn or nullptr
   int n_tokens, n_q_heads, group, nb, nbw;
   float scale_log2;        // softmax_scale * log2(e)
+  int pivot_only;          // 1: only pivot heads run, only their block-mass matrix is written
 };
 
 struct EstParams {
@@ -106,6 +107,8 @@ struct PivotParams {
 };
 
 int sparse_attention_generic(const AttnParams& p, int block_size, int head_dim, cudaStream_t st);
+int sparse_attention_tc5(const AttnParams& p, int n_kv_heads, cudaStream_t st);
+unsigned int tc5_timeout_count();
 int lastblock_profile(const EstParams& p, int head_dim, cudaStream_t st);
 int pool_blocks(const PoolParams& p, int nb, cudaStream_t st);
 int launch_budgets(const BudgetParams& p, cudaStream_t st);

@@ -46,6 +46,7 @@ SIGNATURES = {
     "spf_bitmap_row_counts": (_I, [_P, _I, _I, _P, _P, _P]),
     "spf_sparse_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P,
                                   _P, _I, _P, _P]),
+    "spf_device_timeouts": (_I, []),
     "spf_update_pivots": (_I, [_P, _P, _P, _I, _I, _I, _D, _P]),
 }
 

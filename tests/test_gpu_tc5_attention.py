@@ -1,0 +1,106 @@
+"""The tcgen05/TMEM attention kernel (block_size = head_dim = 128) against the CPU oracle and
+against the generic mma.sync kernel on the same inputs."""
+import math
+import os
+
+import pytest
+import torch
+
+from oracle import spf_oracle as orc
+from shareprefill_b200 import native
+
+pytestmark = pytest.mark.gpu
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+
+
+def _random_sets(nb, h, density, g):
+    sets = []
+    for _ in range(h):
+        m = torch.tril(torch.rand(nb, nb, generator=g) < density)
+        m[:, 0] = True
+        m |= torch.eye(nb, dtype=torch.bool)
+        sets.append(torch.nonzero(m.reshape(-1)).flatten())
+    return sets
+
+
+def _run(q, k, v, bm, kernel):
+    old = os.environ.get("SPF_ATTENTION_KERNEL")
+    if kernel == "generic":
+        os.environ["SPF_ATTENTION_KERNEL"] = "generic"
+    else:
+        os.environ.pop("SPF_ATTENTION_KERNEL", None)
+    try:
+        out = native.sparse_attention(q, k, v, bm, 128, 1.0 / math.sqrt(128))
+        torch.cuda.synchronize()
+    finally:
+        if old is None:
+            os.environ.pop("SPF_ATTENTION_KERNEL", None)
+        else:
+            os.environ["SPF_ATTENTION_KERNEL"] = old
+    return out
+
+
+@pytest.mark.parametrize("n,h,hkv,density", [
+    (640, 4, 2, 0.5),        # two heads per CTA, both K/V reuse paths
+    (1000, 7, 1, 0.4),       # odd group: the last CTA of the group carries a single head; ragged N
+    (2048, 2, 2, 1.0),       # one head per KV head, dense triangle
+    (1536, 8, 2, 0.15),      # sparse rows: heads of a pair visit different columns
+])
+def test_tc5_matches_oracle_and_generic(n, h, hkv, density):
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(n + h)
+    q = torch.randn(n, h, 128, generator=g).bfloat16()
+    k = torch.randn(n, hkv, 128, generator=g).bfloat16()
+    v = torch.randn(n, hkv, 128, generator=g).bfloat16()
+    nb = -(-n // 128)
+    sets = _random_sets(nb, h, density, g)
+    bm = native.sets_to_bitmap(sets, nb, dev)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out_tc5 = _run(qd, kd, vd, bm, "tc5")
+    assert native.load().spf_device_timeouts() == 0, "a bounded wait in the tcgen05 kernel ran out"
+    out_gen = _run(qd, kd, vd, bm, "generic")
+    want, _ = orc.sparse_attention(q, k, v, sets, torch.zeros(h, dtype=torch.bool), 128)
+    for name, got in (("tcgen05", out_tc5), ("generic", out_gen)):
+        err = (got.float().cpu() - want.float()).abs()
+        assert err.max().item() <= MAX_ABS and err.mean().item() <= MEAN_ABS, \
+            (name, err.max().item(), err.mean().item())
+    d = (out_tc5.float() - out_gen.float()).abs()
+    assert d.max().item() <= MAX_ABS
+
+
+def test_tc5_large_logits_trigger_rescale():
+    """Scores that grow along the row force the running maximum to move by far more than the
+    lazy-rescale margin, so the O accumulator in TMEM is rescaled many times."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(5)
+    n, h = 1024, 2
+    q = (torch.randn(n, h, 128, generator=g) * 3).bfloat16()
+    k = torch.randn(n, 1, 128, generator=g)
+    k = (k * torch.linspace(0.2, 4.0, n)[:, None, None]).bfloat16()     # later keys score higher
+    v = torch.randn(n, 1, 128, generator=g).bfloat16()
+    nb = n // 128
+    sets = _random_sets(nb, h, 1.0, g)
+    bm = native.sets_to_bitmap(sets, nb, dev)
+    out = _run(q.to(dev), k.to(dev), v.to(dev), bm, "tc5")
+    assert native.load().spf_device_timeouts() == 0
+    want, _ = orc.sparse_attention(q, k, v, sets, torch.zeros(h, dtype=torch.bool), 128)
+    err = (out.float().cpu() - want.float()).abs()
+    assert err.max().item() <= 4e-2 and err.mean().item() <= MEAN_ABS, (err.max().item(), err.mean().item())
+
+
+def test_tc5_strided_inputs():
+    """[H,N,D]-contiguous tensors seen as [N,H,D] views (head stride N*D) go through TMA unchanged."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(9)
+    n, h, hkv = 768, 4, 2
+    q = torch.randn(h, n, 128, generator=g).bfloat16().to(dev).transpose(0, 1)
+    k = torch.randn(hkv, n, 128, generator=g).bfloat16().to(dev).transpose(0, 1)
+    v = torch.randn(hkv, n, 128, generator=g).bfloat16().to(dev).transpose(0, 1)
+    nb = n // 128
+    sets = _random_sets(nb, h, 0.6, g)
+    bm = native.sets_to_bitmap(sets, nb, dev)
+    out = _run(q, k, v, bm, "tc5")
+    want, _ = orc.sparse_attention(q.cpu().contiguous(), k.cpu().contiguous(), v.cpu().contiguous(), sets,
+                                   torch.zeros(h, dtype=torch.bool), 128)
+    err = (out.float().cpu() - want.float()).abs()
+    assert err.max().item() <= MAX_ABS and err.mean().item() <= MEAN_ABS
