@@ -129,6 +129,51 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 32 consecutive columns of this thread's TMEM lane, no wait (pair with tc_wait_ld)
+__device__ __forceinline__ void tmem_ld32_raw(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+// columns whose index exceeds `last` are masked out (-inf)
+__device__ __forceinline__ void mask_after(uint32_t (&r)[32], int last) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (j > last) r[j] = 0xff800000u;
+}
+__device__ __forceinline__ float row_max(const uint32_t (&r)[32]) {
+  float a = __uint_as_float(r[0]), b = __uint_as_float(r[1]), c = __uint_as_float(r[2]), d = __uint_as_float(r[3]);
+#pragma unroll
+  for (int j = 4; j < 32; j += 4) {
+    a = fmaxf(a, __uint_as_float(r[j]));
+    b = fmaxf(b, __uint_as_float(r[j + 1]));
+    c = fmaxf(c, __uint_as_float(r[j + 2]));
+    d = fmaxf(d, __uint_as_float(r[j + 3]));
+  }
+  return fmaxf(fmaxf(a, b), fmaxf(c, d));
+}
+__device__ __forceinline__ float fast_exp2(float x);
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi);
+// p = 2^(s*scale - m) for 32 scores: packed to bf16 pairs, unrounded values summed into `sum`
+__device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], float scale, float m, uint32_t (&pk)[16], float& sum) {
+  float a = 0.f, b = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), scale, -m));
+    const float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), scale, -m));
+    a += p0;
+    b += p1;
+    pk[j >> 1] = pack2_bf16(p0, p1);
+  }
+  sum += a + b;
+}
+
 // 32 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
@@ -381,18 +426,20 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (!ok) break;
         tc_fence_after();
         const bool diag = (col == r);
-        // pass 1: row maximum of the raw scores
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float v[32];
-          tmem_ld32(tS + c * 32, v);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const bool masked = diag && (c * 32 + j > row);
-            mx = fmaxf(mx, masked ? -INFINITY : v[j]);
-          }
+        // the whole score row (128 fp32) into registers: four loads in flight, one wait
+        uint32_t s0[32], s1[32], s2[32], s3[32];
+        tmem_ld32_raw(tS + 0, s0);
+        tmem_ld32_raw(tS + 32, s1);
+        tmem_ld32_raw(tS + 64, s2);
+        tmem_ld32_raw(tS + 96, s3);
+        tc_wait_ld();
+        if (diag) {   // causal mask inside the diagonal block: key index > query index
+          mask_after(s0, row - 0);
+          mask_after(s1, row - 32);
+          mask_after(s2, row - 64);
+          mask_after(s3, row - 96);
         }
+        const float mx = fmaxf(fmaxf(row_max(s0), row_max(s1)), fmaxf(row_max(s2), row_max(s3)));
         const float mb = mx * p.scale_log2;
         float alpha = 1.f;
         bool grow = false;
@@ -415,22 +462,14 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tmem_st32(tO + c * 32, v);
           }
         }
-        // pass 2: P = 2^(s*scale - m) as bf16 over the first 64 columns of the S region
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          float v[32];
-          tmem_ld32(tS + c * 32, v);
-          uint32_t pk[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const bool m0 = diag && (c * 32 + j > row), m1 = diag && (c * 32 + j + 1 > row);
-            const float p0 = m0 ? 0.f : fast_exp2(fmaf(v[j], p.scale_log2, -m_used));
-            const float p1 = m1 ? 0.f : fast_exp2(fmaf(v[j + 1], p.scale_log2, -m_used));
-            l_sum += p0 + p1;
-            pk[j >> 1] = pack2_bf16(p0, p1);
-          }
-          tmem_st16(tS + c * 16, pk);
-        }
+        // P = 2^(s*scale - m) as bf16 over the first 64 columns of the S region
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        uint32_t pk[16];
+        exp_pack(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tS + 0, pk);
+        exp_pack(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tS + 16, pk);
+        exp_pack(s2, p.scale_log2, m_used, pk, l2); tmem_st16(tS + 32, pk);
+        exp_pack(s3, p.scale_log2, m_used, pk, l3); tmem_st16(tS + 48, pk);
+        l_sum += (l0 + l1) + (l2 + l3);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_pready(h));

@@ -31,8 +31,13 @@ def _lookup_file(tmp_path_factory, lookup, name):
 
 
 def _assert_out_close(got, want):
-    err = (got.float().cpu() - want.float()).abs()
-    assert err.max().item() <= MAX_ABS, f"max abs {err.max().item()}"
+    """max-abs 2e-2 / mean-abs 2e-3; where |want| >= 4 one bf16 ulp (2^-7 relative) already
+    exceeds 2e-2, so a one-ulp difference of the bf16 output is accepted there."""
+    want = want.float()
+    err = (got.float().cpu() - want).abs()
+    bound = torch.maximum(torch.full_like(want, MAX_ABS), want.abs() * 2.0 ** -7)
+    worst = (err - bound).max().item()
+    assert worst <= 0, f"max abs {err.max().item()} (beyond bound by {worst})"
     assert err.mean().item() <= MEAN_ABS, f"mean abs {err.mean().item()}"
 
 

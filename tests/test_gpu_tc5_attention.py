@@ -13,6 +13,17 @@ pytestmark = pytest.mark.gpu
 MAX_ABS, MEAN_ABS = 2e-2, 2e-3
 
 
+def _assert_out_close(got, want, name=""):
+    """max-abs 2e-2 / mean-abs 2e-3; where |want| >= 4 one bf16 ulp (2^-7 relative) already
+    exceeds 2e-2, so a one-ulp difference of the bf16 output is accepted there."""
+    want = want.float()
+    err = (got.float().cpu() - want).abs()
+    bound = torch.maximum(torch.full_like(want, MAX_ABS), want.abs() * 2.0 ** -7)
+    worst = (err - bound).max().item()
+    assert worst <= 0, f"{name}: max abs {err.max().item()} (beyond bound by {worst})"
+    assert err.mean().item() <= MEAN_ABS, f"{name}: mean abs {err.mean().item()}"
+
+
 def _random_sets(nb, h, density, g):
     sets = []
     for _ in range(h):
@@ -61,9 +72,7 @@ def test_tc5_matches_oracle_and_generic(n, h, hkv, density):
     out_gen = _run(qd, kd, vd, bm, "generic")
     want, _ = orc.sparse_attention(q, k, v, sets, torch.zeros(h, dtype=torch.bool), 128)
     for name, got in (("tcgen05", out_tc5), ("generic", out_gen)):
-        err = (got.float().cpu() - want.float()).abs()
-        assert err.max().item() <= MAX_ABS and err.mean().item() <= MEAN_ABS, \
-            (name, err.max().item(), err.mean().item())
+        _assert_out_close(got, want, name)
     d = (out_tc5.float() - out_gen.float()).abs()
     assert d.max().item() <= MAX_ABS
 
@@ -84,8 +93,7 @@ def test_tc5_large_logits_trigger_rescale():
     out = _run(q.to(dev), k.to(dev), v.to(dev), bm, "tc5")
     assert native.load().spf_device_timeouts() == 0
     want, _ = orc.sparse_attention(q, k, v, sets, torch.zeros(h, dtype=torch.bool), 128)
-    err = (out.float().cpu() - want.float()).abs()
-    assert err.max().item() <= 4e-2 and err.mean().item() <= MEAN_ABS, (err.max().item(), err.mean().item())
+    _assert_out_close(out, want, "rescale")
 
 
 def test_tc5_strided_inputs():
@@ -102,5 +110,4 @@ def test_tc5_strided_inputs():
     out = _run(q, k, v, bm, "tc5")
     want, _ = orc.sparse_attention(q.cpu().contiguous(), k.cpu().contiguous(), v.cpu().contiguous(), sets,
                                    torch.zeros(h, dtype=torch.bool), 128)
-    err = (out.float().cpu() - want.float()).abs()
-    assert err.max().item() <= MAX_ABS and err.mean().item() <= MEAN_ABS
+    _assert_out_close(out, want, "strided")
