@@ -5,7 +5,8 @@
 // tile fetched by TMA serves both heads (GQA reuse); the two heads ping-pong on the tensor pipe.
 //
 //   warp 0      TMA producer: Q tiles once, then K and V tiles of the union of both heads' bitmap
-//               rows through a 2-stage ring (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//               rows through a 3-deep K ring and a 2-deep V ring (cp.async.bulk.tensor, 128-byte
+//               swizzle, no multicast)
 //   warp 1      MMA issuer: S_h = Q_h K^T (both operands in shared memory) and O_h += P_h V
 //               (P_h read from TMEM, V from shared memory) with tcgen05.mma, accumulators in TMEM;
 //               completion is signalled to mbarriers with tcgen05.commit
@@ -29,16 +30,28 @@ namespace spf {
 constexpr int TC_BS = 128;
 constexpr int TC_D = 128;
 constexpr int TC_THREADS = 320;
-constexpr int TC_STAGES = 2;
+constexpr int TC_KSTAGES = 3;
+constexpr int TC_VSTAGES = 2;
 constexpr uint32_t TC_TILE_BYTES = TC_BS * TC_D * 2;        // 32 KiB: one 128x128 bf16 tile
 constexpr uint32_t TC_SLAB_BYTES = TC_TILE_BYTES / 2;       // [128 rows][64 elements]
-constexpr uint32_t TC_SMEM_Q = 0;                           // 2 tiles
-constexpr uint32_t TC_SMEM_KV = 2 * TC_TILE_BYTES;          // per stage: K tile, V tile
-constexpr uint32_t TC_SMEM_BAR = TC_SMEM_KV + TC_STAGES * 2 * TC_TILE_BYTES;
-constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_BAR + 256;
+// shared memory map: 1 KiB of control data, then 1024-byte aligned tiles (Q x2, K x3, V x2)
+constexpr uint32_t TC_SMEM_CTRL = 0;                        // mbarriers, TMEM slot, abort flag
+constexpr uint32_t TC_SMEM_Q = 1024;
+constexpr uint32_t TC_SMEM_K = TC_SMEM_Q + 2 * TC_TILE_BYTES;
+constexpr uint32_t TC_SMEM_V = TC_SMEM_K + TC_KSTAGES * TC_TILE_BYTES;
+constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_V + TC_VSTAGES * TC_TILE_BYTES;   // 225 KiB of the 227 KiB limit
 constexpr float TC_RESCALE_LOG2 = 8.0f;
 
 static __device__ unsigned int g_tc5_timeouts = 0;
+
+// Timing probe, compiled in only with -DSPF_TC5_TRACE: clock64() stamps of the first CTA's
+// first 64 iterations, [role: softmax A, softmax B, MMA issuer][iteration][slot].
+#ifdef SPF_TC5_TRACE
+__device__ long long g_tc5_trace[3][64][8];
+#define TRACE(role, it, slot) do { if (blockIdx.x == 0 && (it) < 64) g_tc5_trace[role][it][slot] = clock64(); } while (0)
+#else
+#define TRACE(role, it, slot) do {} while (0)
+#endif
 
 struct Tc5Params {
   __nv_bfloat16* out;
@@ -271,21 +284,24 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const Tc5Params p) {
   // once several waits have run out the kernel is not making progress: later CTAs do nothing
   if (*reinterpret_cast<volatile unsigned int*>(&g_tc5_timeouts) > 16u) return;
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // the swizzled tiles need 1024-byte alignment; the launch reserves 1 KiB of slack for it
-  unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+  extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t sbase = smem_addr(smem);
-  // barriers
-  const uint32_t bar0 = sbase + TC_SMEM_BAR;
+  if (sbase & 1023u) {   // the swizzled tiles need a 1024-byte aligned base (no static shared memory here)
+    if (threadIdx.x == 0) atomicAdd(&g_tc5_timeouts, 1000u);
+    return;
+  }
+  // control region
+  const uint32_t bar0 = sbase + TC_SMEM_CTRL;
   const uint32_t bar_q = bar0;
   auto bar_kfull = [&](int s) { return bar0 + 8u * (1 + s); };
-  auto bar_vfull = [&](int s) { return bar0 + 8u * (3 + s); };
-  auto bar_kvempty = [&](int s) { return bar0 + 8u * (5 + s); };
-  auto bar_sfull = [&](int h) { return bar0 + 8u * (7 + h); };
-  auto bar_pready = [&](int h) { return bar0 + 8u * (9 + h); };
-  auto bar_odone = [&](int h) { return bar0 + 8u * (11 + h); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_SMEM_BAR + 8 * 13);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_SMEM_BAR + 8 * 13 + 8);
+  auto bar_kempty = [&](int s) { return bar0 + 8u * (4 + s); };
+  auto bar_vfull = [&](int s) { return bar0 + 8u * (7 + s); };
+  auto bar_vempty = [&](int s) { return bar0 + 8u * (9 + s); };
+  auto bar_sfull = [&](int h) { return bar0 + 8u * (11 + h); };
+  auto bar_pready = [&](int h) { return bar0 + 8u * (13 + h); };
+  auto bar_odone = [&](int h) { return bar0 + 8u * (15 + h); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_SMEM_CTRL + 8 * 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_SMEM_CTRL + 8 * 17 + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // heavy (late) query blocks first
@@ -302,7 +318,8 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
-    for (int s = 0; s < TC_STAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_vfull(s), 1); mbar_init(bar_kvempty(s), 1); }
+    for (int s = 0; s < TC_KSTAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_kempty(s), 1); }
+    for (int s = 0; s < TC_VSTAGES; ++s) { mbar_init(bar_vfull(s), 1); mbar_init(bar_vempty(s), 1); }
     for (int h = 0; h < 2; ++h) { mbar_init(bar_sfull(h), 1); mbar_init(bar_pready(h), 128); mbar_init(bar_odone(h), 1); }
     *abort_flag = 0;
     fence_barrier_init();
@@ -325,48 +342,63 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tma_load_3d(dst, &map_q, bar_q, 0, row0, hA + h);
         tma_load_3d(dst + TC_SLAB_BYTES, &map_q, bar_q, 64, row0, hA + h);
       }
-      PairWalker wk; wk.init(rowA, rowB, r);
-      int fl, i = 0, issued = 0;
-      for (int col = wk.next(fl); col >= 0; col = wk.next(fl), ++i) {
-        const int s = i & 1;
-        if (!mbar_wait(bar_kvempty(s), ((i >> 1) & 1) ^ 1, abort_flag)) break;
-        const uint32_t kdst = sbase + TC_SMEM_KV + s * 2 * TC_TILE_BYTES;
-        const uint32_t vdst = kdst + TC_TILE_BYTES;
+      auto load_k = [&](int i, int col) -> bool {
+        const int s = i % TC_KSTAGES;
+        if (!mbar_wait(bar_kempty(s), ((i / TC_KSTAGES) & 1) ^ 1, abort_flag)) return false;
+        const uint32_t dst = sbase + TC_SMEM_K + s * TC_TILE_BYTES;
         mbar_expect_tx(bar_kfull(s), TC_TILE_BYTES);
-        tma_load_3d(kdst, &map_k, bar_kfull(s), 0, col * TC_BS, kvh);
-        tma_load_3d(kdst + TC_SLAB_BYTES, &map_k, bar_kfull(s), 64, col * TC_BS, kvh);
+        tma_load_3d(dst, &map_k, bar_kfull(s), 0, col * TC_BS, kvh);
+        tma_load_3d(dst + TC_SLAB_BYTES, &map_k, bar_kfull(s), 64, col * TC_BS, kvh);
+        return true;
+      };
+      auto load_v = [&](int i, int col) -> bool {
+        const int s = i % TC_VSTAGES;
+        if (!mbar_wait(bar_vempty(s), ((i / TC_VSTAGES) & 1) ^ 1, abort_flag)) return false;
+        const uint32_t dst = sbase + TC_SMEM_V + s * TC_TILE_BYTES;
         mbar_expect_tx(bar_vfull(s), TC_TILE_BYTES);
-        tma_load_3d(vdst, &map_v, bar_vfull(s), 0, col * TC_BS, kvh);
-        tma_load_3d(vdst + TC_SLAB_BYTES, &map_v, bar_vfull(s), 64, col * TC_BS, kvh);
-        issued = i + 1;
+        tma_load_3d(dst, &map_v, bar_vfull(s), 0, col * TC_BS, kvh);
+        tma_load_3d(dst + TC_SLAB_BYTES, &map_v, bar_vfull(s), 64, col * TC_BS, kvh);
+        return true;
+      };
+      // K runs one column ahead of V: K(i+1) is requested before V(i)
+      PairWalker wk; wk.init(rowA, rowB, r);
+      int fl, i = 0, k_issued = 0, v_issued = 0;
+      int col = wk.next(fl);
+      bool ok = true;
+      if (col >= 0) { ok = load_k(0, col); k_issued = ok ? 1 : 0; }
+      while (ok && col >= 0) {
+        const int ncol = wk.next(fl);
+        if (ncol >= 0) { ok = load_k(i + 1, ncol); if (ok) k_issued = i + 2; }
+        if (ok) { ok = load_v(i, col); if (ok) v_issued = i + 1; }
+        col = ncol; ++i;
       }
       // drain: every copy this thread started must have landed before the CTA may exit
       mbar_wait(bar_q, 0, abort_flag, true);
-      for (int j = (issued >= 2 ? issued - 2 : 0); j < issued; ++j) {
-        mbar_wait(bar_kfull(j & 1), (j >> 1) & 1, abort_flag, true);
-        mbar_wait(bar_vfull(j & 1), (j >> 1) & 1, abort_flag, true);
-      }
+      for (int j = (k_issued >= TC_KSTAGES ? k_issued - TC_KSTAGES : 0); j < k_issued; ++j)
+        mbar_wait(bar_kfull(j % TC_KSTAGES), (j / TC_KSTAGES) & 1, abort_flag, true);
+      for (int j = (v_issued >= TC_VSTAGES ? v_issued - TC_VSTAGES : 0); j < v_issued; ++j)
+        mbar_wait(bar_vfull(j % TC_VSTAGES), (j / TC_VSTAGES) & 1, abort_flag, true);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t tS[2] = {tmem + 0u, tmem + 128u};
       const uint32_t tO[2] = {tmem + 256u, tmem + 384u};
-      auto issue_qk = [&](int h, int s) {
-        const uint32_t qa = sbase + TC_SMEM_Q + h * TC_TILE_BYTES;
-        const uint32_t ka = sbase + TC_SMEM_KV + s * 2 * TC_TILE_BYTES;
+      const uint64_t qd[2] = {desc_kmajor(sbase + TC_SMEM_Q), desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES)};
+      auto issue_qk = [&](int h, int ks_stage) {
+        const uint64_t kd = desc_kmajor(sbase + TC_SMEM_K + ks_stage * TC_TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * TC_SLAB_BYTES + (ks & 3) * 32;
-          mma_ss(tS[h], desc_kmajor(qa + off), desc_kmajor(ka + off), TC_IDESC_QK, ks > 0);
+          const uint64_t off = uint64_t(((ks >> 2) * TC_SLAB_BYTES + (ks & 3) * 32) >> 4);
+          mma_ss(tS[h], qd[h] + off, kd + off, TC_IDESC_QK, ks > 0);
         }
         tc_commit(bar_sfull(h));
       };
-      auto issue_pv = [&](int h, int s, bool accumulate) {
-        const uint32_t va = sbase + TC_SMEM_KV + s * 2 * TC_TILE_BYTES + TC_TILE_BYTES;
+      auto issue_pv = [&](int h, int vs_stage, bool accumulate) {
+        const uint64_t vd = desc_mnmajor(sbase + TC_SMEM_V + vs_stage * TC_TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tO[h], tS[h] + ks * 8, desc_mnmajor(va + ks * 2048), TC_IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
+          mma_ts(tO[h], tS[h] + ks * 8, vd + uint64_t((ks * 2048) >> 4), TC_IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
       };
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       PairWalker wk; wk.init(rowA, rowB, r);
@@ -377,28 +409,37 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (ok && col >= 0) {
         ok = mbar_wait(bar_kfull(0), 0, abort_flag);
         tc_fence_after();
-        if (ok) for (int h = 0; h < 2; ++h) if (fl & (1 << h)) issue_qk(h, 0);
+        if (ok) {
+          for (int h = 0; h < 2; ++h) if (fl & (1 << h)) issue_qk(h, 0);
+          tc_commit(bar_kempty(0));
+        }
       }
       while (ok && col >= 0) {
         const int ncol = wk.next(nfl);
-        const int s = i & 1, ns = (i + 1) & 1;
+        const int vs = i % TC_VSTAGES, nks = (i + 1) % TC_KSTAGES;
         bool v_ready = false, nk_ready = false;
         const int last_h = (fl & 2) ? 1 : 0;
+        const int nlast_h = (nfl & 2) ? 1 : 0;
         for (int h = 0; h < 2 && ok; ++h) {
           if (fl & (1 << h)) {
-            if (!v_ready) { ok = mbar_wait(bar_vfull(s), (i >> 1) & 1, abort_flag); v_ready = true; }
+            if (!v_ready) { ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
+            if (h == 0) TRACE(2, i, 0); else TRACE(2, i, 4);
             if (ok) ok = mbar_wait(bar_pready(h), nblk[h] & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            issue_pv(h, s, nblk[h] > 0);
+            if (h == 0) TRACE(2, i, 1); else TRACE(2, i, 5);
+            issue_pv(h, vs, nblk[h] > 0);
+            if (h == 0) TRACE(2, i, 2); else TRACE(2, i, 6);
             ++nblk[h];
-            if (h == last_h) tc_commit(bar_kvempty(s));
+            if (h == last_h) tc_commit(bar_vempty(vs));
           }
           if (ncol >= 0 && (nfl & (1 << h))) {
-            if (!nk_ready) { ok = mbar_wait(bar_kfull(ns), ((i + 1) >> 1) & 1, abort_flag); nk_ready = true; }
+            if (!nk_ready) { ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
             if (!ok) break;
             tc_fence_after();
-            issue_qk(h, ns);
+            issue_qk(h, nks);
+            if (h == nlast_h) tc_commit(bar_kempty(nks));
+            if (h == 0) TRACE(2, i, 3); else TRACE(2, i, 7);
           }
         }
         col = ncol; fl = nfl; ++i;
@@ -422,9 +463,11 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       PairWalker wk; wk.init(h == 0 ? rowA : rowB, nullptr, r);
       int fl;
       for (int col = wk.next(fl); col >= 0 && ok; col = wk.next(fl), ++k) {
+        if (lane == 0 && quarter == 0) TRACE(h, k, 0);
         ok = mbar_wait(bar_sfull(h), k & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        if (lane == 0 && quarter == 0) TRACE(h, k, 1);
         const bool diag = (col == r);
         // the whole score row (128 fp32) into registers: four loads in flight, one wait
         uint32_t s0[32], s1[32], s2[32], s3[32];
@@ -433,6 +476,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tmem_ld32_raw(tS + 64, s2);
         tmem_ld32_raw(tS + 96, s3);
         tc_wait_ld();
+        if (lane == 0 && quarter == 0) TRACE(h, k, 2);
         if (diag) {   // causal mask inside the diagonal block: key index > query index
           mask_after(s0, row - 0);
           mask_after(s1, row - 32);
@@ -470,9 +514,11 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         exp_pack(s2, p.scale_log2, m_used, pk, l2); tmem_st16(tS + 32, pk);
         exp_pack(s3, p.scale_log2, m_used, pk, l3); tmem_st16(tS + 48, pk);
         l_sum += (l0 + l1) + (l2 + l3);
+        if (lane == 0 && quarter == 0) TRACE(h, k, 3);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_pready(h));
+        if (lane == 0 && quarter == 0) TRACE(h, k, 4);
       }
       // ---- epilogue
       const int tok = row0 + row;
@@ -558,12 +604,16 @@ int sparse_attention_tc5(const AttnParams& a, int n_kv_heads, cudaStream_t st) {
   p.n_kv_heads = n_kv_heads; p.group = a.group; p.pairs = (a.group + 1) / 2; p.nb = a.nb; p.nbw = a.nbw;
   p.scale_log2 = a.scale_log2;
   cudaError_t e = cudaFuncSetAttribute(sparse_attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       int(TC_SMEM_TOTAL + 1024));
+                                       int(TC_SMEM_TOTAL));
   if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
   const unsigned grid = unsigned(a.nb) * unsigned(n_kv_heads) * unsigned(p.pairs);
-  sparse_attn_tc5_kernel<<<grid, TC_THREADS, TC_SMEM_TOTAL + 1024, st>>>(mq, mk, mv, p);
+  sparse_attn_tc5_kernel<<<grid, TC_THREADS, TC_SMEM_TOTAL, st>>>(mq, mk, mv, p);
   return check_launch();
 }
+
+#ifdef SPF_TC5_TRACE
+extern "C" void spf_tc5_trace_dump(long long* out) { cudaMemcpyFromSymbol(out, g_tc5_trace, sizeof(long long) * 3 * 64 * 8); }
+#endif
 
 unsigned int tc5_timeout_count() {
   unsigned int v = 0;
