@@ -82,6 +82,17 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// non-blocking probe: the MMA issuer is a single thread on the critical path and polls instead of
+// letting the hardware suspend it
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -97,6 +108,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try(bar, parity)) return true;
     if ((++spins & 63) == 0) {
       if (*abort_flag && !drain) return false;
+      if (global_ns() - t0 > 1000000000ull) {
+        *abort_flag = 1;
+        atomicAdd(&g_tc5_timeouts, 1u);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_test(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  int spins = 0;
+  while (true) {
+    if (mbar_test(bar, parity)) return true;
+    if ((++spins & 1023) == 0) {
+      if (*abort_flag) return false;
       if (global_ns() - t0 > 1000000000ull) {
         *abort_flag = 1;
         atomicAdd(&g_tc5_timeouts, 1u);
@@ -160,31 +187,63 @@ __device__ __forceinline__ void mask_after(uint32_t (&r)[32], int last) {
   for (int j = 0; j < 32; ++j)
     if (j > last) r[j] = 0xff800000u;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float row_max(const uint32_t (&r)[32]) {
-  float a = __uint_as_float(r[0]), b = __uint_as_float(r[1]), c = __uint_as_float(r[2]), d = __uint_as_float(r[3]);
+  float a = __uint_as_float(r[0]), b = __uint_as_float(r[1]);
 #pragma unroll
-  for (int j = 4; j < 32; j += 4) {
-    a = fmaxf(a, __uint_as_float(r[j]));
-    b = fmaxf(b, __uint_as_float(r[j + 1]));
-    c = fmaxf(c, __uint_as_float(r[j + 2]));
-    d = fmaxf(d, __uint_as_float(r[j + 3]));
+  for (int j = 2; j < 30; j += 4) {
+    a = max3(a, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+    b = max3(b, __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
   }
-  return fmaxf(fmaxf(a, b), fmaxf(c, d));
+  return max3(fmaxf(a, b), __uint_as_float(r[30]), __uint_as_float(r[31]));
 }
 __device__ __forceinline__ float fast_exp2(float x);
-__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi);
+// two fp32 lanes in one 64-bit register (packed fp32x2 arithmetic of sm_100)
+__device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
+  unsigned long long d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+  return d;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float& lo, float& hi) {
+  uint32_t a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+  lo = __uint_as_float(a); hi = __uint_as_float(b);
+}
+__device__ __forceinline__ unsigned long long f2_fma(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_from(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));   // first source -> upper half
+  return d;
+}
 // p = 2^(s*scale - m) for 32 scores: packed to bf16 pairs, unrounded values summed into `sum`
 __device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], float scale, float m, uint32_t (&pk)[16], float& sum) {
-  float a = 0.f, b = 0.f;
+  const unsigned long long sc2 = f2_pack(scale, scale), nm2 = f2_pack(-m, -m);
+  unsigned long long acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
   for (int j = 0; j < 32; j += 2) {
-    const float p0 = fast_exp2(fmaf(__uint_as_float(r[j]), scale, -m));
-    const float p1 = fast_exp2(fmaf(__uint_as_float(r[j + 1]), scale, -m));
-    a += p0;
-    b += p1;
-    pk[j >> 1] = pack2_bf16(p0, p1);
+    const unsigned long long x = f2_pack(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+    float y0, y1;
+    f2_unpack(f2_fma(x, sc2, nm2), y0, y1);
+    const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+    acc[(j >> 1) & 3] = f2_add(acc[(j >> 1) & 3], f2_pack(p0, p1));
+    pk[j >> 1] = bf16x2_from(p0, p1);
   }
-  sum += a + b;
+  float a0, a1;
+  f2_unpack(f2_add(f2_add(acc[0], acc[1]), f2_add(acc[2], acc[3])), a0, a1);
+  sum += a0 + a1;
 }
 
 // 32 consecutive fp32 columns of this thread's TMEM lane
@@ -382,23 +441,41 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t tS[2] = {tmem + 0u, tmem + 128u};
-      const uint32_t tO[2] = {tmem + 256u, tmem + 384u};
-      const uint64_t qd[2] = {desc_kmajor(sbase + TC_SMEM_Q), desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES)};
-      auto issue_qk = [&](int h, int ks_stage) {
-        const uint64_t kd = desc_kmajor(sbase + TC_SMEM_K + ks_stage * TC_TILE_BYTES);
+      // every descriptor is built once; the issue loops below are 8 back-to-back tcgen05.mma each
+      uint64_t qdA[8], qdB[8], kdesc[TC_KSTAGES], vdesc[TC_VSTAGES];
+      uint32_t koff[8], voff[8];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t off = uint64_t(((ks >> 2) * TC_SLAB_BYTES + (ks & 3) * 32) >> 4);
-          mma_ss(tS[h], qd[h] + off, kd + off, TC_IDESC_QK, ks > 0);
+      for (int ks = 0; ks < 8; ++ks) {
+        koff[ks] = ((ks >> 2) * TC_SLAB_BYTES + (ks & 3) * 32) >> 4;
+        voff[ks] = (ks * 2048) >> 4;
+        qdA[ks] = desc_kmajor(sbase + TC_SMEM_Q) + koff[ks];
+        qdB[ks] = desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES) + koff[ks];
+      }
+#pragma unroll
+      for (int s = 0; s < TC_KSTAGES; ++s) kdesc[s] = desc_kmajor(sbase + TC_SMEM_K + s * TC_TILE_BYTES);
+#pragma unroll
+      for (int s = 0; s < TC_VSTAGES; ++s) vdesc[s] = desc_mnmajor(sbase + TC_SMEM_V + s * TC_TILE_BYTES);
+      auto issue_qk = [&](int h, int ks_stage) {
+        const uint64_t kd = ks_stage == 0 ? kdesc[0] : (ks_stage == 1 ? kdesc[1] : kdesc[2]);
+        if (h == 0) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) mma_ss(tmem + 0u, qdA[ks], kd + koff[ks], TC_IDESC_QK, ks > 0);
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) mma_ss(tmem + 128u, qdB[ks], kd + koff[ks], TC_IDESC_QK, ks > 0);
         }
         tc_commit(bar_sfull(h));
       };
       auto issue_pv = [&](int h, int vs_stage, bool accumulate) {
-        const uint64_t vd = desc_mnmajor(sbase + TC_SMEM_V + vs_stage * TC_TILE_BYTES);
+        const uint64_t vd = vs_stage == 0 ? vdesc[0] : vdesc[1];
+        const uint32_t acc0 = accumulate ? 1u : 0u;
+        if (h == 0) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tO[h], tS[h] + ks * 8, vd + uint64_t((ks * 2048) >> 4), TC_IDESC_PV, (accumulate || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 8; ++ks) mma_ts(tmem + 256u, tmem + 0u + ks * 8, vd + voff[ks], TC_IDESC_PV, ks > 0 ? 1u : acc0);
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) mma_ts(tmem + 384u, tmem + 128u + ks * 8, vd + voff[ks], TC_IDESC_PV, ks > 0 ? 1u : acc0);
+        }
       };
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       PairWalker wk; wk.init(rowA, rowB, r);
@@ -422,9 +499,9 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int nlast_h = (nfl & 2) ? 1 : 0;
         for (int h = 0; h < 2 && ok; ++h) {
           if (fl & (1 << h)) {
-            if (!v_ready) { ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
+            if (!v_ready) { ok = mbar_spin(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
             if (h == 0) TRACE(2, i, 0); else TRACE(2, i, 4);
-            if (ok) ok = mbar_wait(bar_pready(h), nblk[h] & 1, abort_flag);
+            if (ok) ok = mbar_spin(bar_pready(h), nblk[h] & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             if (h == 0) TRACE(2, i, 1); else TRACE(2, i, 5);
@@ -434,7 +511,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (h == last_h) tc_commit(bar_vempty(vs));
           }
           if (ncol >= 0 && (nfl & (1 << h))) {
-            if (!nk_ready) { ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
+            if (!nk_ready) { ok = mbar_spin(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
             if (!ok) break;
             tc_fence_after();
             issue_qk(h, nks);

@@ -52,21 +52,30 @@ __device__ __forceinline__ void est_load_q(const EstParams& p, int h, uint32_t s
   __syncthreads();
 }
 
-// Load key tile `tile` of the head's KV head into shared memory at sk and compute
-// S = Q K^T rounded to bf16 with the causal mask.  Ends with all warps past their reads of sk.
+// exp(x) through ex2.approx: the logits were rounded to bf16 already, a 2-ulp exponential is ample
+__device__ __forceinline__ float est_exp(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+
+// Start the asynchronous copy of key tile `tile` of the head's KV head into shared memory at sk.
 template <int D>
-__device__ __forceinline__ void est_tile_scores(const EstParams& p, int h, int tile, uint32_t sk,
-                                                const uint32_t (&qf)[D / 16][4],
-                                                float (&s)[EST_COLS / 8][4]) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+__device__ __forceinline__ void est_issue_tile(const EstParams& p, int h, int tile, uint32_t sk) {
   const int kvh = h / p.group;
   const int c0 = tile * EST_COLS;
-  const int q0 = p.n_tokens - p.rq;
   load_tile_async<EST_COLS, D, EST_NT>(sk, p.k + int64_t(kvh) * p.k_sh + int64_t(c0) * p.k_sn, p.k_sn,
-                                       min(EST_COLS, p.n_tokens - c0), tid);
-  cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
+                                       min(EST_COLS, p.n_tokens - c0), threadIdx.x);
+}
+
+// S = Q K^T for the key tile resident at sk, rounded to bf16, with the causal mask.
+template <int D>
+__device__ __forceinline__ void est_tile_scores(const EstParams& p, int tile, uint32_t sk,
+                                                const uint32_t (&qf)[D / 16][4],
+                                                float (&s)[EST_COLS / 8][4]) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c0 = tile * EST_COLS;
+  const int q0 = p.n_tokens - p.rq;
 #pragma unroll
   for (int j = 0; j < EST_COLS / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
 #pragma unroll
@@ -80,15 +89,22 @@ __device__ __forceinline__ void est_tile_scores(const EstParams& p, int h, int t
       mma_bf16_16816(s[2 * jp + 1], qf[ks], bf[2], bf[3]);
     }
   }
-  __syncthreads();
   const int row_lo = warp * 16 + (lane >> 2);
+  if (c0 + EST_COLS - 1 <= q0) {   // tile entirely before the first query: no mask needed
 #pragma unroll
-  for (int j = 0; j < EST_COLS / 8; ++j) {
+    for (int j = 0; j < EST_COLS / 8; ++j) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int kpos = c0 + j * 8 + (lane & 3) * 2 + (e & 1);
-      const int qpos = q0 + row_lo + (e >> 1) * 8;
-      s[j][e] = (kpos > qpos) ? -INFINITY : bf16_round(s[j][e]);
+      for (int e = 0; e < 4; ++e) s[j][e] = bf16_round(s[j][e]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < EST_COLS / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int kpos = c0 + j * 8 + (lane & 3) * 2 + (e & 1);
+        const int qpos = q0 + row_lo + (e >> 1) * 8;
+        s[j][e] = (kpos > qpos) ? -INFINITY : bf16_round(s[j][e]);
+      }
     }
   }
 }
@@ -96,15 +112,24 @@ __device__ __forceinline__ void est_tile_scores(const EstParams& p, int h, int t
 template <int D>
 __global__ void __launch_bounds__(EST_NT) lastblock_stats_kernel(const EstParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  const uint32_t sbase = smem_u32(smem);
+  constexpr uint32_t TILE = EST_ROWS * D * 2;
+  const uint32_t sbase = smem_u32(smem);      // two key tile buffers; the second stages Q first
   const int h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t_begin = blockIdx.x * p.tiles_per_cta;
+  const int t_end = min(p.ntiles, t_begin + p.tiles_per_cta);
+  est_issue_tile<D>(p, h, t_begin, sbase);
+  cp_async_commit();
   uint32_t qf[D / 16][4];
-  est_load_q<D>(p, h, sbase, qf);
-  const int t_end = min(p.ntiles, (int(blockIdx.x) + 1) * p.tiles_per_cta);
-  for (int tile = blockIdx.x * p.tiles_per_cta; tile < t_end; ++tile) {
+  est_load_q<D>(p, h, sbase + TILE, qf);
+  for (int tile = t_begin; tile < t_end; ++tile) {
+    const int buf = (tile - t_begin) & 1;
+    if (tile + 1 < t_end) est_issue_tile<D>(p, h, tile + 1, sbase + (buf ^ 1) * TILE);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
     float s[EST_COLS / 8][4];
-    est_tile_scores<D>(p, h, tile, sbase, qf, s);
+    est_tile_scores<D>(p, tile, sbase + buf * TILE, qf, s);
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < EST_COLS / 8; ++j) {
@@ -121,8 +146,8 @@ __global__ void __launch_bounds__(EST_NT) lastblock_stats_kernel(const EstParams
     const float m1 = (mx[1] == -INFINITY) ? 0.f : mx[1];
 #pragma unroll
     for (int j = 0; j < EST_COLS / 8; ++j) {
-      sum[0] += expf(s[j][0] - m0) + expf(s[j][1] - m0);
-      sum[1] += expf(s[j][2] - m1) + expf(s[j][3] - m1);
+      sum[0] += est_exp(s[j][0] - m0) + est_exp(s[j][1] - m0);
+      sum[1] += est_exp(s[j][2] - m1) + est_exp(s[j][3] - m1);
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -137,7 +162,9 @@ __global__ void __launch_bounds__(EST_NT) lastblock_stats_kernel(const EstParams
       p.part_m[base + row + 8] = mx[1];
       p.part_l[base + row + 8] = sum[1];
     }
+    __syncthreads();   // everyone is done with this buffer before it is refilled
   }
+  cp_async_wait<0>();
 }
 
 __global__ void lastblock_reduce_kernel(const EstParams p) {
@@ -149,7 +176,7 @@ __global__ void lastblock_reduce_kernel(const EstParams p) {
   double z = 0.0;
   for (int t = 0; t < p.ntiles; ++t) {
     const float mt = pm[int64_t(t) * EST_ROWS];
-    if (mt != -INFINITY) z += static_cast<double>(pl[int64_t(t) * EST_ROWS]) * static_cast<double>(expf(mt - m));
+    if (mt != -INFINITY) z += static_cast<double>(pl[int64_t(t) * EST_ROWS]) * static_cast<double>(est_exp(mt - m));
   }
   p.row_m[h * EST_ROWS + row] = m;
   p.row_z[h * EST_ROWS + row] = static_cast<float>(z);
@@ -158,62 +185,83 @@ __global__ void lastblock_reduce_kernel(const EstParams p) {
 template <int D>
 __global__ void __launch_bounds__(EST_NT) lastblock_profile_kernel(const EstParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int LD = EST_COLS + 1;
-  constexpr int P_BYTES = ((EST_ROWS * LD * 4 + 127) / 128) * 128;
-  float* P = reinterpret_cast<float*>(smem);            // [128][129] fp32
-  const uint32_t sk = smem_u32(smem) + P_BYTES;         // K tile (also stages Q once)
+  // P rows are 136 floats apart: the 8-byte stores of the MMA fragment layout (4 rows x 8 columns per
+  // half warp) then fall into distinct banks; column and anti-diagonal reads are conflict free anyway
+  constexpr int LD = EST_COLS + 8;
+  constexpr uint32_t P_BYTES = EST_ROWS * LD * 4;
+  constexpr uint32_t TILE = EST_ROWS * D * 2;
+  float* P = reinterpret_cast<float*>(smem);            // [128][136] fp32
+  const uint32_t sk = smem_u32(smem) + P_BYTES;         // two key tile buffers; the second stages Q first
   const int h = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t_begin = blockIdx.x * p.tiles_per_cta;
+  const int t_end = min(p.ntiles, t_begin + p.tiles_per_cta);
+  est_issue_tile<D>(p, h, t_begin, sk);
+  cp_async_commit();
   uint32_t qf[D / 16][4];
-  est_load_q<D>(p, h, sk, qf);
+  est_load_q<D>(p, h, sk + TILE, qf);
   const int row_lo = warp * 16 + (lane >> 2);
   const float M0 = p.row_m[h * EST_ROWS + row_lo], M1 = p.row_m[h * EST_ROWS + row_lo + 8];
-  const float Z0 = p.row_z[h * EST_ROWS + row_lo], Z1 = p.row_z[h * EST_ROWS + row_lo + 8];
+  const float R0 = 1.0f / p.row_z[h * EST_ROWS + row_lo], R1 = 1.0f / p.row_z[h * EST_ROWS + row_lo + 8];
   const int rq = p.rq;
   const float inv_rows = 1.0f / static_cast<float>(rq);
-  const int t_end = min(p.ntiles, (int(blockIdx.x) + 1) * p.tiles_per_cta);
-  for (int tile = blockIdx.x * p.tiles_per_cta; tile < t_end; ++tile) {
+  for (int tile = t_begin; tile < t_end; ++tile) {
+    const int buf = (tile - t_begin) & 1;
+    if (tile + 1 < t_end) est_issue_tile<D>(p, h, tile + 1, sk + (buf ^ 1) * TILE);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();   // the tile has landed; the previous tile's sums are done reading P
     float s[EST_COLS / 8][4];
-    est_tile_scores<D>(p, h, tile, sk, qf, s);
+    est_tile_scores<D>(p, tile, sk + buf * TILE, qf, s);
 #pragma unroll
     for (int j = 0; j < EST_COLS / 8; ++j) {
       const int c = j * 8 + (lane & 3) * 2;
-      P[row_lo * LD + c] = expf(s[j][0] - M0) / Z0;
-      P[row_lo * LD + c + 1] = expf(s[j][1] - M0) / Z0;
-      P[(row_lo + 8) * LD + c] = expf(s[j][2] - M1) / Z1;
-      P[(row_lo + 8) * LD + c + 1] = expf(s[j][3] - M1) / Z1;
+      *reinterpret_cast<float2*>(&P[row_lo * LD + c]) =
+          make_float2(est_exp(s[j][0] - M0) * R0, est_exp(s[j][1] - M0) * R0);
+      *reinterpret_cast<float2*>(&P[(row_lo + 8) * LD + c]) =
+          make_float2(est_exp(s[j][2] - M1) * R1, est_exp(s[j][3] - M1) * R1);
     }
     __syncthreads();
     const int c0 = tile * EST_COLS;
-    if (tid < EST_COLS && c0 + tid < p.n_tokens) {
-      float acc = 0.f;
-      for (int i = 0; i < rq; ++i) acc += P[i * LD + tid];
-      p.vertical[int64_t(h) * p.n_tokens + c0 + tid] = acc * inv_rows;
-    }
-    // anti-diagonals: element (i, jj) lands on tile-local index t = jj + (rq-1) - i
+    // anti-diagonals first (255 of them): element (i, jj) lands on tile-local index t = jj + (rq-1) - i
     for (int t = tid; t < EST_COLS + rq - 1; t += EST_NT) {
       const int i_lo = max(0, rq - 1 - t);
       const int i_hi = min(rq - 1, EST_COLS - 1 + rq - 1 - t);
-      float acc = 0.f;
-      for (int i = i_lo; i <= i_hi; ++i) acc += P[i * LD + (t - (rq - 1) + i)];
+      float a0 = 0.f, a1 = 0.f;
+      int i = i_lo;
+      for (; i + 1 <= i_hi; i += 2) {
+        a0 += P[i * LD + (t - (rq - 1) + i)];
+        a1 += P[(i + 1) * LD + (t - (rq - 1) + i + 1)];
+      }
+      if (i <= i_hi) a0 += P[i * LD + (t - (rq - 1) + i)];
       const int n = c0 + t;
-      if (n < p.n_tokens) atomicAdd(&p.slash[int64_t(h) * p.n_tokens + n], acc * inv_rows);
+      if (n < p.n_tokens) atomicAdd(&p.slash[int64_t(h) * p.n_tokens + n], (a0 + a1) * inv_rows);
     }
-    __syncthreads();
+    // column sums: two threads per column (even / odd rows), combined with a shuffle
+    {
+      const int col = tid >> 1, par = tid & 1;
+      float acc = 0.f;
+      for (int i = par; i < rq; i += 2) acc += P[i * LD + col];
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      if (par == 0 && c0 + col < p.n_tokens) p.vertical[int64_t(h) * p.n_tokens + c0 + col] = acc * inv_rows;
+    }
   }
+  cp_async_wait<0>();
 }
 
 template <int D>
 static int launch_estimate(const EstParams& p, cudaStream_t st) {
   const dim3 grid(ceil_div(p.ntiles, p.tiles_per_cta), p.n_q_heads);
   constexpr int TILE = EST_ROWS * D * 2;
-  constexpr int P_BYTES = ((EST_ROWS * (EST_COLS + 1) * 4 + 127) / 128) * 128;
+  constexpr int P_BYTES = EST_ROWS * (EST_COLS + 8) * 4;
   cudaError_t e;
-  e = cudaFuncSetAttribute(lastblock_profile_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_BYTES + TILE);
+  e = cudaFuncSetAttribute(lastblock_stats_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * TILE);
   if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
-  lastblock_stats_kernel<D><<<grid, EST_NT, TILE, st>>>(p);
+  e = cudaFuncSetAttribute(lastblock_profile_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_BYTES + 2 * TILE);
+  if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
+  lastblock_stats_kernel<D><<<grid, EST_NT, 2 * TILE, st>>>(p);
   lastblock_reduce_kernel<<<p.n_q_heads, EST_ROWS, 0, st>>>(p);
-  lastblock_profile_kernel<D><<<grid, EST_NT, P_BYTES + TILE, st>>>(p);
+  lastblock_profile_kernel<D><<<grid, EST_NT, P_BYTES + 2 * TILE, st>>>(p);
   return check_launch();
 }
 

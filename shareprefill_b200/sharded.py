@@ -29,12 +29,42 @@ def kv_group_shard(num_q_heads: int, num_kv_heads: int, rank: int, world: int) -
     return rank * per * g, (rank + 1) * per * g, rank * per, (rank + 1) * per
 
 
+SUMMARY_FIELDS = ("vs_ratio", "pivot_vertical", "pivot_slash", "pattern")
+
+
+def pack_pivot_summaries(state, layer: int, h0: int, h1: int) -> torch.Tensor:
+    """int32 ``[S, 1 + widths]``: for every slot whose pivot was elected in ``layer`` among heads
+    ``[h0, h1)`` a leading 1 and the summary fields' raw bits, zeros elsewhere."""
+    f = state.field
+    s = max(state.n_slots, 1)
+    mine = (f("pivot_layer") == layer) & (f("pivot_head") >= h0) & (f("pivot_head") < h1)
+    cols = [mine.to(torch.int32).view(s, 1)] + [f(n).view(torch.int32).reshape(s, -1) for n in SUMMARY_FIELDS]
+    packed = torch.cat(cols, dim=1)
+    return torch.where(mine.view(s, 1), packed, torch.zeros_like(packed))
+
+
+def merge_pivot_summaries(state, gathered: torch.Tensor) -> None:
+    """Install the summaries of ``gathered [ranks, S, width]`` (at most one rank contributes per
+    slot) into the local state and mark those patterns ready."""
+    f = state.field
+    s = max(state.n_slots, 1)
+    merged = gathered.sum(0)
+    new = merged[:, 0] > 0
+    o = 1
+    for name in SUMMARY_FIELDS:
+        dst = f(name).view(torch.int32).reshape(s, -1)
+        width = dst.shape[1]
+        dst.copy_(torch.where(new.view(s, 1), merged[:, o:o + width], dst))
+        o += width
+    ready = f("pattern_ready")
+    ready.copy_(torch.where(new, torch.ones_like(ready), ready))
+
+
 class HeadShardExchange:
     def __init__(self, head_begin: int, head_end: int, group=None):
         self.h0, self.h1 = head_begin, head_end
         self.group = group
         self.world = dist.get_world_size(group)
-        self.launches = 0
 
     def gather_heads(self, local: torch.Tensor) -> torch.Tensor:
         """All ranks' per-head values in global head order (equal shard sizes)."""
@@ -46,23 +76,7 @@ class HeadShardExchange:
         st = sharing.state
         if st is None or st.n_slots == 0:
             return
-        f = st.field
-        head, lay = f("pivot_head"), f("pivot_layer")
-        mine = (lay == layer) & (head >= self.h0) & (head < self.h1)          # [S] bool
-        s = st.n_slots
-        fl = [f("vs_ratio").view(torch.int32).view(s, 1), f("pivot_vertical").view(torch.int32),
-              f("pivot_slash").view(torch.int32), f("pattern").reshape(s, -1)]
-        packed = torch.cat([mine.to(torch.int32).view(s, 1)] + fl, dim=1)
-        packed = torch.where(mine.view(s, 1), packed, torch.zeros_like(packed))
-        gathered = torch.empty(self.world, *packed.shape, dtype=packed.dtype, device=packed.device)
-        dist.all_gather_into_tensor(gathered, packed, group=self.group)
-        merged = gathered.sum(0)                     # at most one rank contributes per slot
-        new = merged[:, 0] > 0
-        nb = st.nb
-        o = 1
-        upd = [("vs_ratio", 1), ("pivot_vertical", nb), ("pivot_slash", nb), ("pattern", fl[3].shape[1])]
-        for name, width in upd:
-            dst = f(name).view(torch.int32).reshape(s, -1)
-            dst.copy_(torch.where(new.view(s, 1), merged[:, o:o + width], dst))
-            o += width
-        f("pattern_ready").copy_(torch.where(new, torch.ones_like(lay), f("pattern_ready")))
+        packed = pack_pivot_summaries(st, layer, self.h0, self.h1)
+        flat = torch.empty(self.world * packed.numel(), dtype=packed.dtype, device=packed.device)
+        dist.all_gather_into_tensor(flat, packed.reshape(-1), group=self.group)
+        merge_pivot_summaries(st, flat.view(self.world, *packed.shape))

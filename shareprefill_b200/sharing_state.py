@@ -153,6 +153,17 @@ class AttentionSharing:
         ``stage_inputs`` (tests) replaces computed intermediates by given tensors:
         ``vertical``/``slash`` ``[H,N]``, ``avg_qk`` ``[H,nb]``, ``qa_scores`` ``[H,nb,nb]``.
         """
+        ctx = self.profile_heads(q, k, layer_idx, num_heads, block_size, min_budget, max_budget,
+                                 pattern_threshold, gqa_interleave, stage_inputs)
+        jsd_qa_all = ctx["jsd_qa"] if self.exchange is None else self.exchange.gather_heads(ctx["jsd_qa"])
+        return self.select_blocks(ctx, jsd_qa_all, similarity_threshold, fallback_threshold,
+                                  queryaware_threshold)
+
+    def profile_heads(self, q, k, layer_idx, num_heads, block_size, min_budget, max_budget,
+                      pattern_threshold=0.9, gqa_interleave=False, stage_inputs=None) -> dict:
+        """First half of ``get_active_blocks``: everything that is independent per head (pooling,
+        last-block profile, budgets, pooled last-row estimate, divergences).  The returned context
+        carries ``jsd_qa`` - the one per-head value every rank needs from every other rank."""
         if gqa_interleave:
             raise NotImplementedError("gqa_interleave=True is not supported by the B200 kernels")
         if q.dim() == 4:
@@ -164,9 +175,8 @@ class AttentionSharing:
         dev = q.device
         state = self._ensure_state(nb, dev)
         h0 = 0 if self.head_range is None else self.head_range[0]
-        h_total = num_heads if self.head_range is None else num_heads
-        slot_all = self._slot_table(layer_idx, h_total, dev)
-        slot_local = slot_all[h0:h0 + h] if (h0 or h != h_total) else slot_all
+        slot_all = self._slot_table(layer_idx, num_heads, dev)
+        slot_local = slot_all[h0:h0 + h] if (h0 or h != num_heads) else slot_all
         si = stage_inputs or {}
 
         avg_q, avg_k = native.pool_qk(q, k, block_size)
@@ -181,20 +191,29 @@ class AttentionSharing:
                                                       min_budget, max_blocks)
         avg_qk = si["avg_qk"] if "avg_qk" in si else native.pooled_last_row(q, avg_k, block_size)
         jsd_qa, jsd_v, jsd_s = native.classify_heads(avg_qk, vpool, spool, slot_local, state)
-        jsd_qa_all = jsd_qa if self.exchange is None else self.exchange.gather_heads(jsd_qa)
-        flags = native.elect_and_share(jsd_qa_all, slot_all, h0, jsd_v, jsd_s, vpool, spool, state,
-                                       layer_idx, queryaware_threshold, similarity_threshold,
-                                       fallback_threshold, min_budget, nv, ns)
-        bitmap = native.build_vs_bitmap(vpool, spool, nv, ns, flags, slot_local, state)
-        if "qa_scores" in si:
-            scores = si["qa_scores"]
-        else:
-            scores = native.query_aware_scores(avg_q, avg_k, flags)
-        native.query_aware_select(scores, flags, pattern_threshold, bitmap)
-        pat = BlockPattern(bitmap, flags, slot_local, nb, nv, ns,
-                           info=dict(vertical=vertical, slash=slash, vpool=vpool, spool=spool,
-                                     avg_qk=avg_qk, avg_k=avg_k, avg_q=avg_q, jsd_qa=jsd_qa,
-                                     jsd_v=jsd_v, jsd_s=jsd_s))
+        return dict(layer=layer_idx, nb=nb, h0=h0, state=state, slot_all=slot_all, slot_local=slot_local,
+                    avg_q=avg_q, avg_k=avg_k, vertical=vertical, slash=slash, nv=nv, ns=ns, vpool=vpool,
+                    spool=spool, avg_qk=avg_qk, jsd_qa=jsd_qa, jsd_v=jsd_v, jsd_s=jsd_s,
+                    min_blocks=min_budget, pattern_threshold=pattern_threshold,
+                    qa_scores=si.get("qa_scores"))
+
+    def select_blocks(self, ctx: dict, jsd_qa_all: torch.Tensor, similarity_threshold=0.5,
+                      fallback_threshold=0.9, queryaware_threshold=0.1):
+        """Second half: election / sharing over ALL heads' divergences, then this instance's
+        heads' patterns.  Returns ``(BlockPattern, use_dense[1,H])``."""
+        state = ctx["state"]
+        nv, ns, vpool, spool = ctx["nv"], ctx["ns"], ctx["vpool"], ctx["spool"]
+        flags = native.elect_and_share(jsd_qa_all, ctx["slot_all"], ctx["h0"], ctx["jsd_v"], ctx["jsd_s"],
+                                       vpool, spool, state, ctx["layer"], queryaware_threshold,
+                                       similarity_threshold, fallback_threshold, ctx["min_blocks"], nv, ns)
+        bitmap = native.build_vs_bitmap(vpool, spool, nv, ns, flags, ctx["slot_local"], state)
+        scores = ctx["qa_scores"]
+        if scores is None:
+            scores = native.query_aware_scores(ctx["avg_q"], ctx["avg_k"], flags)
+        native.query_aware_select(scores, flags, ctx["pattern_threshold"], bitmap)
+        pat = BlockPattern(bitmap, flags, ctx["slot_local"], ctx["nb"], nv, ns,
+                           info={k_: ctx[k_] for k_ in ("vertical", "slash", "vpool", "spool", "avg_qk",
+                                                        "avg_k", "avg_q", "jsd_qa", "jsd_v", "jsd_s")})
         self.last_pattern = pat
         self._mark("select")
         return pat, pat.use_dense
