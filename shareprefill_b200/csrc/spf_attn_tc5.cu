@@ -82,17 +82,6 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// non-blocking probe: the MMA issuer is a single thread on the critical path and polls instead of
-// letting the hardware suspend it
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -108,22 +97,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try(bar, parity)) return true;
     if ((++spins & 63) == 0) {
       if (*abort_flag && !drain) return false;
-      if (global_ns() - t0 > 1000000000ull) {
-        *abort_flag = 1;
-        atomicAdd(&g_tc5_timeouts, 1u);
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ bool mbar_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_test(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
-  int spins = 0;
-  while (true) {
-    if (mbar_test(bar, parity)) return true;
-    if ((++spins & 1023) == 0) {
-      if (*abort_flag) return false;
       if (global_ns() - t0 > 1000000000ull) {
         *abort_flag = 1;
         atomicAdd(&g_tc5_timeouts, 1u);
@@ -499,9 +472,9 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int nlast_h = (nfl & 2) ? 1 : 0;
         for (int h = 0; h < 2 && ok; ++h) {
           if (fl & (1 << h)) {
-            if (!v_ready) { ok = mbar_spin(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
+            if (!v_ready) { ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
             if (h == 0) TRACE(2, i, 0); else TRACE(2, i, 4);
-            if (ok) ok = mbar_spin(bar_pready(h), nblk[h] & 1, abort_flag);
+            if (ok) ok = mbar_wait(bar_pready(h), nblk[h] & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
             if (h == 0) TRACE(2, i, 1); else TRACE(2, i, 5);
@@ -511,7 +484,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (h == last_h) tc_commit(bar_vempty(vs));
           }
           if (ncol >= 0 && (nfl & (1 << h))) {
-            if (!nk_ready) { ok = mbar_spin(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
+            if (!nk_ready) { ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
             if (!ok) break;
             tc_fence_after();
             issue_qk(h, nks);
