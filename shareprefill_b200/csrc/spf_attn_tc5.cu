@@ -10,11 +10,13 @@
 //   warp 1      MMA issuer: S_h = Q_h K^T (both operands in shared memory) and O_h += P_h V
 //               (P_h read from TMEM, V from shared memory) with tcgen05.mma, accumulators in TMEM;
 //               completion is signalled to mbarriers with tcgen05.commit
-//   warps 2-5   softmax warpgroup of head A: a thread owns one query row; tcgen05.ld of S, base-2
+//   warps 2-3   idle (they only complete the control warpgroup, which gives most of its registers
+//               to the softmax warpgroups with setmaxnreg)
+//   warps 4-7   softmax warpgroup of head A: a thread owns one query row; tcgen05.ld of S, base-2
 //               online softmax with scale*log2(e) folded in, P rounded to bf16 and written back
 //               over S with tcgen05.st, O rescaled in TMEM only when the running maximum moved by
 //               more than 2^8 (exact: the final normalisation uses the same reference point)
-//   warps 6-9   the same for head B
+//   warps 8-11  the same for head B
 //
 // TMEM (512 columns): S_A/P_A [0,128)  S_B/P_B [128,256)  O_A [256,384)  O_B [384,512).
 // Arithmetic matches block_wise_prefill_attention_kernel (attn/shareprefill_attn.py:381-471):
@@ -29,7 +31,7 @@ namespace spf {
 
 constexpr int TC_BS = 128;
 constexpr int TC_D = 128;
-constexpr int TC_THREADS = 320;
+constexpr int TC_THREADS = 384;                             // 3 warpgroups: control, softmax A, softmax B
 constexpr int TC_KSTAGES = 3;
 constexpr int TC_VSTAGES = 2;
 constexpr uint32_t TC_TILE_BYTES = TC_BS * TC_D * 2;        // 32 KiB: one 128x128 bf16 tile
@@ -336,11 +338,12 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_SMEM_CTRL + 8 * 17 + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // heavy (late) query blocks first
+  // CTAs that run at the same time belong to the same KV head (its K/V stream stays in L2);
+  // within a KV head the heavy (late) query blocks go first
   int bid = blockIdx.x;
   const int pair = bid % p.pairs; bid /= p.pairs;
-  const int kvh = bid % p.n_kv_heads; bid /= p.n_kv_heads;
-  const int r = p.nb - 1 - bid;
+  const int r = p.nb - 1 - (bid % p.nb);
+  const int kvh = bid / p.nb;
   const int hA = kvh * p.group + pair * 2;
   const bool hasB = (pair * 2 + 1) < p.group;
   const int hB = hasB ? hA + 1 : -1;
@@ -365,6 +368,9 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  if (warp < 4) {
+    // control warpgroup (producer, MMA issuer, two idle warps) hands registers to the softmax warpgroups
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -414,41 +420,27 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // every descriptor is built once; the issue loops below are 8 back-to-back tcgen05.mma each
-      uint64_t qdA[8], qdB[8], kdesc[TC_KSTAGES], vdesc[TC_VSTAGES];
-      uint32_t koff[8], voff[8];
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        koff[ks] = ((ks >> 2) * TC_SLAB_BYTES + (ks & 3) * 32) >> 4;
-        voff[ks] = (ks * 2048) >> 4;
-        qdA[ks] = desc_kmajor(sbase + TC_SMEM_Q) + koff[ks];
-        qdB[ks] = desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES) + koff[ks];
-      }
-#pragma unroll
-      for (int s = 0; s < TC_KSTAGES; ++s) kdesc[s] = desc_kmajor(sbase + TC_SMEM_K + s * TC_TILE_BYTES);
-#pragma unroll
-      for (int s = 0; s < TC_VSTAGES; ++s) vdesc[s] = desc_mnmajor(sbase + TC_SMEM_V + s * TC_TILE_BYTES);
+      // descriptors differ from a base only in the 14-bit address field: one 64-bit add per operand
+      const uint64_t qdA = desc_kmajor(sbase + TC_SMEM_Q), qdB = desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES);
+      const uint64_t kd0 = desc_kmajor(sbase + TC_SMEM_K), vd0 = desc_mnmajor(sbase + TC_SMEM_V);
       auto issue_qk = [&](int h, int ks_stage) {
-        const uint64_t kd = ks_stage == 0 ? kdesc[0] : (ks_stage == 1 ? kdesc[1] : kdesc[2]);
-        if (h == 0) {
+        const uint64_t kd = kd0 + uint64_t((ks_stage * TC_TILE_BYTES) >> 4);
+        const uint64_t qd = h == 0 ? qdA : qdB;
+        const uint32_t ts = tmem + (h == 0 ? 0u : 128u);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) mma_ss(tmem + 0u, qdA[ks], kd + koff[ks], TC_IDESC_QK, ks > 0);
-        } else {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) mma_ss(tmem + 128u, qdB[ks], kd + koff[ks], TC_IDESC_QK, ks > 0);
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t off = uint64_t(((ks >> 2) * TC_SLAB_BYTES + (ks & 3) * 32) >> 4);
+          mma_ss(ts, qd + off, kd + off, TC_IDESC_QK, ks > 0);
         }
         tc_commit(bar_sfull(h));
       };
       auto issue_pv = [&](int h, int vs_stage, bool accumulate) {
-        const uint64_t vd = vs_stage == 0 ? vdesc[0] : vdesc[1];
+        const uint64_t vd = vd0 + uint64_t((vs_stage * TC_TILE_BYTES) >> 4);
+        const uint32_t ts = tmem + (h == 0 ? 0u : 128u), to = tmem + (h == 0 ? 256u : 384u);
         const uint32_t acc0 = accumulate ? 1u : 0u;
-        if (h == 0) {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) mma_ts(tmem + 256u, tmem + 0u + ks * 8, vd + voff[ks], TC_IDESC_PV, ks > 0 ? 1u : acc0);
-        } else {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) mma_ts(tmem + 384u, tmem + 128u + ks * 8, vd + voff[ks], TC_IDESC_PV, ks > 0 ? 1u : acc0);
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ts(to, ts + ks * 8, vd + uint64_t((ks * 2048) >> 4), TC_IDESC_PV, ks > 0 ? 1u : acc0);
       };
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       PairWalker wk; wk.init(rowA, rowB, r);
@@ -497,9 +489,11 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_commit(bar_odone(0));
       tc_commit(bar_odone(1));
     }
+  }
   } else {
     // ------------------------------------------------------------ softmax warpgroups
-    const int h = (warp - 2) >> 2;                 // 0: head A, 1: head B
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const int h = (warp - 4) >> 2;                 // 0: head A, 1: head B
     const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;           // query row within the block
     const int head = h == 0 ? hA : hB;

@@ -191,6 +191,7 @@ __global__ void __launch_bounds__(EST_NT) lastblock_profile_kernel(const EstPara
   constexpr uint32_t P_BYTES = EST_ROWS * LD * 4;
   constexpr uint32_t TILE = EST_ROWS * D * 2;
   float* P = reinterpret_cast<float*>(smem);            // [128][136] fp32
+  __shared__ float colpart[EST_COLS];
   const uint32_t sk = smem_u32(smem) + P_BYTES;         // two key tile buffers; the second stages Q first
   const int h = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -237,13 +238,16 @@ __global__ void __launch_bounds__(EST_NT) lastblock_profile_kernel(const EstPara
       const int n = c0 + t;
       if (n < p.n_tokens) atomicAdd(&p.slash[int64_t(h) * p.n_tokens + n], (a0 + a1) * inv_rows);
     }
-    // column sums: two threads per column (even / odd rows), combined with a shuffle
+    // column sums: warps 0-3 take the even rows, warps 4-7 the odd rows (consecutive lanes read
+    // consecutive columns), halves combined through shared memory
     {
-      const int col = tid >> 1, par = tid & 1;
+      const int col = tid & (EST_COLS - 1), par = tid >> 7;
       float acc = 0.f;
       for (int i = par; i < rq; i += 2) acc += P[i * LD + col];
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (par == 0 && c0 + col < p.n_tokens) p.vertical[int64_t(h) * p.n_tokens + c0 + col] = acc * inv_rows;
+      if (par == 1) colpart[col] = acc;
+      __syncthreads();
+      if (par == 0 && c0 + col < p.n_tokens)
+        p.vertical[int64_t(h) * p.n_tokens + c0 + col] = (acc + colpart[col]) * inv_rows;
     }
   }
   cp_async_wait<0>();
