@@ -42,6 +42,10 @@ STAGES = ["pool", "profile", "select", "attention", "pivot_update"]
 # kernels launched per layer by each stage (this library's own kernels)
 LAUNCHES_PER_LAYER = {"pool": 1, "profile": 3, "select": 7, "attention": 1, "pivot_update": 2}
 DISTINCT_LAYER_INPUTS = 4   # host/device inputs are drawn for this many layers and cycled
+# DRAM bytes (read + write) of ONE launch of the block-sparse attention kernel, from ncu captures of
+# these workloads on one GPU (profiles/sparse_attn_tc5_cfg1_and_cfg2.md); None where not captured
+ATTENTION_DRAM_BYTES_PER_LAUNCH = {("cfg2", 131072, 1.0): 3039617280 + 1056879104,
+                                   ("cfg1", 32768, 1.0): 403427072 + 234135296}
 
 
 def measured_peaks():
@@ -386,10 +390,13 @@ def run_gpu_arm(args, wl):
         "stage_ms_rank0": stage_ms,
         "roofline": {"kernel": "block-sparse attention", "bound": "tensor", "achieved": achieved_tf,
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved_tf / peaks["tflops"],
-                     "traffic": None, "of": peaks["source"]},
+                     "traffic": ATTENTION_DRAM_BYTES_PER_LAUNCH.get((wl.name, wl.seq_len, wl.q_gain)) if world == 1 else None,
+                     "traffic_unit": "bytes per launch (ncu dram read+write)", "of": peaks["source"]},
         "roofline_pool": {"kernel": "Q/K block pooling", "bound": "hbm", "achieved": pool_gbs,
                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": pool_gbs / peaks["hbm_gbs"],
-                          "traffic": None, "of": peaks["source"]},
+                          "traffic": {131072: 1342209280 + 10450176, 32768: 335595008 + 6505472}.get(wl.seq_len)
+                          if (world == 1 and wl.num_q_heads == 32 and wl.num_kv_heads == 8) else None,
+                          "traffic_unit": "bytes per launch (ncu dram read+write)", "of": peaks["source"]},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
         "gpu_launches": launches * args.steps,

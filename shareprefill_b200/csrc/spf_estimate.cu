@@ -183,37 +183,34 @@ __global__ void lastblock_reduce_kernel(const EstParams p) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(EST_NT) lastblock_profile_kernel(const EstParams p) {
+__global__ void __launch_bounds__(EST_NT, 2) lastblock_profile_kernel(const EstParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   // P rows are 136 floats apart: the 8-byte stores of the MMA fragment layout (4 rows x 8 columns per
-  // half warp) then fall into distinct banks; column and anti-diagonal reads are conflict free anyway
+  // half warp) then fall into distinct banks; column and anti-diagonal reads are conflict free anyway.
+  // One key tile buffer only: two CTAs share an SM and cover each other's load and reduction phases.
   constexpr int LD = EST_COLS + 8;
   constexpr uint32_t P_BYTES = EST_ROWS * LD * 4;
-  constexpr uint32_t TILE = EST_ROWS * D * 2;
   float* P = reinterpret_cast<float*>(smem);            // [128][136] fp32
   __shared__ float colpart[EST_COLS];
-  const uint32_t sk = smem_u32(smem) + P_BYTES;         // two key tile buffers; the second stages Q first
+  const uint32_t sk = smem_u32(smem) + P_BYTES;         // key tile; stages Q first
   const int h = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int t_begin = blockIdx.x * p.tiles_per_cta;
   const int t_end = min(p.ntiles, t_begin + p.tiles_per_cta);
-  est_issue_tile<D>(p, h, t_begin, sk);
-  cp_async_commit();
   uint32_t qf[D / 16][4];
-  est_load_q<D>(p, h, sk + TILE, qf);
+  est_load_q<D>(p, h, sk, qf);
   const int row_lo = warp * 16 + (lane >> 2);
   const float M0 = p.row_m[h * EST_ROWS + row_lo], M1 = p.row_m[h * EST_ROWS + row_lo + 8];
   const float R0 = 1.0f / p.row_z[h * EST_ROWS + row_lo], R1 = 1.0f / p.row_z[h * EST_ROWS + row_lo + 8];
   const int rq = p.rq;
   const float inv_rows = 1.0f / static_cast<float>(rq);
   for (int tile = t_begin; tile < t_end; ++tile) {
-    const int buf = (tile - t_begin) & 1;
-    if (tile + 1 < t_end) est_issue_tile<D>(p, h, tile + 1, sk + (buf ^ 1) * TILE);
+    est_issue_tile<D>(p, h, tile, sk);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<0>();
     __syncthreads();   // the tile has landed; the previous tile's sums are done reading P
     float s[EST_COLS / 8][4];
-    est_tile_scores<D>(p, tile, sk + buf * TILE, qf, s);
+    est_tile_scores<D>(p, tile, sk, qf, s);
 #pragma unroll
     for (int j = 0; j < EST_COLS / 8; ++j) {
       const int c = j * 8 + (lane & 3) * 2;
@@ -222,35 +219,40 @@ __global__ void __launch_bounds__(EST_NT) lastblock_profile_kernel(const EstPara
       *reinterpret_cast<float2*>(&P[(row_lo + 8) * LD + c]) =
           make_float2(est_exp(s[j][2] - M1) * R1, est_exp(s[j][3] - M1) * R1);
     }
-    __syncthreads();
+    __syncthreads();   // P complete; every warp is also done reading the key tile
     const int c0 = tile * EST_COLS;
     // anti-diagonals first (255 of them): element (i, jj) lands on tile-local index t = jj + (rq-1) - i
     for (int t = tid; t < EST_COLS + rq - 1; t += EST_NT) {
       const int i_lo = max(0, rq - 1 - t);
       const int i_hi = min(rq - 1, EST_COLS - 1 + rq - 1 - t);
-      float a0 = 0.f, a1 = 0.f;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      const float* base = P + (t - (rq - 1));
       int i = i_lo;
-      for (; i + 1 <= i_hi; i += 2) {
-        a0 += P[i * LD + (t - (rq - 1) + i)];
-        a1 += P[(i + 1) * LD + (t - (rq - 1) + i + 1)];
+      for (; i + 3 <= i_hi; i += 4) {
+        a0 += base[i * (LD + 1)];
+        a1 += base[(i + 1) * (LD + 1)];
+        a2 += base[(i + 2) * (LD + 1)];
+        a3 += base[(i + 3) * (LD + 1)];
       }
-      if (i <= i_hi) a0 += P[i * LD + (t - (rq - 1) + i)];
+      for (; i <= i_hi; ++i) a0 += base[i * (LD + 1)];
       const int n = c0 + t;
-      if (n < p.n_tokens) atomicAdd(&p.slash[int64_t(h) * p.n_tokens + n], (a0 + a1) * inv_rows);
+      if (n < p.n_tokens) atomicAdd(&p.slash[int64_t(h) * p.n_tokens + n], ((a0 + a1) + (a2 + a3)) * inv_rows);
     }
     // column sums: warps 0-3 take the even rows, warps 4-7 the odd rows (consecutive lanes read
     // consecutive columns), halves combined through shared memory
     {
       const int col = tid & (EST_COLS - 1), par = tid >> 7;
-      float acc = 0.f;
-      for (int i = par; i < rq; i += 2) acc += P[i * LD + col];
+      float b0 = 0.f, b1 = 0.f;
+      int i = par;
+      for (; i + 2 < rq; i += 4) { b0 += P[i * LD + col]; b1 += P[(i + 2) * LD + col]; }
+      for (; i < rq; i += 2) b0 += P[i * LD + col];
+      const float acc = b0 + b1;
       if (par == 1) colpart[col] = acc;
       __syncthreads();
       if (par == 0 && c0 + col < p.n_tokens)
         p.vertical[int64_t(h) * p.n_tokens + c0 + col] = (acc + colpart[col]) * inv_rows;
     }
   }
-  cp_async_wait<0>();
 }
 
 template <int D>
@@ -261,11 +263,11 @@ static int launch_estimate(const EstParams& p, cudaStream_t st) {
   cudaError_t e;
   e = cudaFuncSetAttribute(lastblock_stats_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * TILE);
   if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
-  e = cudaFuncSetAttribute(lastblock_profile_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_BYTES + 2 * TILE);
+  e = cudaFuncSetAttribute(lastblock_profile_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_BYTES + TILE);
   if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
   lastblock_stats_kernel<D><<<grid, EST_NT, 2 * TILE, st>>>(p);
   lastblock_reduce_kernel<<<p.n_q_heads, EST_ROWS, 0, st>>>(p);
-  lastblock_profile_kernel<D><<<grid, EST_NT, P_BYTES + 2 * TILE, st>>>(p);
+  lastblock_profile_kernel<D><<<grid, EST_NT, P_BYTES + TILE, st>>>(p);
   return check_launch();
 }
 
