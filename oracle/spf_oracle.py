@@ -11,12 +11,16 @@ computes between the Hugging Face attention interface and the attention output:
                arithmetic) and :226-269 (CSR offsets)
 * pivot state- shareprefill/attn/attention_sharing.py:94-103 (``update_pivotal_attns``)
 
-Pinning.  The reference has no tests and no golden vectors.  The selection part
-of this oracle is pinned against outputs of the reference's own selection code
-imported and run on CPU (``tests/golden/make_golden.py`` -> ``tests/golden/*.npz``).
-The attention part restates a Triton kernel that cannot run without a GPU:
-its parity is UNPINNED against the reference itself; it is cross-checked only
-against a dense fp32 softmax attention restricted to the same block mask.
+Pinning.  The reference has no tests and no golden vectors of its own, so the oracle is
+pinned against outputs of the reference's code itself:
+* selection: the reference's ``get_active_blocks`` / ``update_pivotal_attns`` / helpers imported
+  and run on CPU (``tests/golden/make_golden.py`` -> ``tests/golden/*.npz``): every block set,
+  flag, pivot pattern and vs_ratio is reproduced exactly;
+* attention, CSR offsets, pooling: the reference's Triton kernels run unmodified on a B200
+  (``tests/golden/make_golden_triton.py`` -> ``tests/golden/triton_kernels.npz``): attention
+  outputs agree within the path's bf16 tolerance (max-abs 2e-2 / mean-abs 2e-3), block-mass
+  matrices within 2e-3, CSR offsets exactly; the pooled means differ from the Triton kernel's
+  by its bf16 reduction-tree rounding (this restatement sums in fp32).
 
 The arithmetic follows torch CPU semantics the reference inherits: ``cumsum`` on
 fp32 accumulates in fp64 and rounds every prefix to fp32; comparisons against a
