@@ -196,6 +196,74 @@ def run_reference_arm(args, wl):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------------ reference on the GPU
+def run_reference_triton_arm(args, wl):
+    """Informational arm: the UNMODIFIED reference (its torch selection code and Triton kernels, from
+    the offline install under baseline/_ref) on the same GPU and the same inputs, one GPU only.
+    Not the contract's reference arm (that one is the CPU port); it shows the incumbent GPU path."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "shareprefill")):
+        print(json.dumps({"impl": "reference-triton", "unavailable": "baseline/_ref is not installed"}))
+        return
+    sys.path.insert(0, ref_dir)
+    from shareprefill.attn import shareprefill_attn as ref_attn
+    from shareprefill.attn.attention_sharing import AttentionSharing as RefSharing
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    lookup_path = workload_lookup(wl)
+    if lookup_path.endswith("_table.json"):      # the reference reads its own JSON layout only
+        from shareprefill_b200.clusters.convert_lookup import from_table
+        with open(lookup_path) as f:
+            lk = from_table(json.load(f))
+        tmp = tempfile.NamedTemporaryFile("w", suffix=".json", delete=False)
+        json.dump(lk, tmp)
+        tmp.close()
+        lookup_path = tmp.name
+    sharing = RefSharing(lookup_path)
+    L, nd, g = wl.num_layers, min(DISTINCT_LAYER_INPUTS, wl.num_layers), wl.group_size
+    bs = wl.block_size
+    inputs = []
+    for i in range(nd):
+        q, k, v = make_qkv(wl, i, device="cuda")
+        inputs.append((q[None].contiguous(), k.repeat_interleave(g, dim=1)[None].contiguous(),
+                       v.repeat_interleave(g, dim=1)[None].contiguous()))
+    stage = {"select": 0.0, "attention": 0.0, "pivot_update": 0.0}
+
+    def step(record):
+        sharing.reset_state()
+        for layer in range(L):
+            q, k, v = inputs[layer % nd]
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record()
+            block_idx, use_dense = sharing.get_active_blocks(
+                q, k, layer, wl.num_q_heads, bs, math.ceil(wl.min_budget / bs), 2**31 - 1,
+                wl.pattern_threshold, wl.similarity_threshold, wl.fallback_threshold, wl.queryaware_threshold, False)
+            ev[1].record()
+            o, avg = ref_attn.triton_block_wise_prefill_attention(q, k, v, block_idx, use_dense, bs)
+            ev[2].record()
+            sharing.update_pivotal_attns(layer, avg, use_dense, wl.pattern_threshold)
+            ev[3].record()
+            if record:
+                torch.cuda.synchronize()
+                for name, a, b in (("select", 0, 1), ("attention", 1, 2), ("pivot_update", 2, 3)):
+                    stage[name] += ev[a].elapsed_time(ev[b])
+
+    for _ in range(args.warmup):
+        step(False)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step(True)
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    print(json.dumps({"impl": "reference-triton", "metric": "sparse_prefill_attention_ms_per_forward", "value": ms,
+                      "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                      "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+                      "config": config_dict(wl, 1), "stage_ms": {k_: v_ / args.steps for k_, v_ in stage.items()},
+                      "note": "K/V repeated to the query-head count as the reference's entry point does; the repeat "
+                              "and the [B,N,H,D] copies it makes are outside this timing"}))
+
+
 # ------------------------------------------------------------------------------ GPU arm
 def run_gpu_arm(args, wl):
     import torch.distributed as dist
@@ -412,7 +480,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-triton"])
     ap.add_argument("--workload", default="cfg2")
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--seq-len", type=int, default=None)
@@ -428,6 +496,8 @@ def main():
         wl = wl.replace(q_gain=args.q_gain)
     if args.impl == "reference":
         run_reference_arm(args, wl)
+    elif args.impl == "reference-triton":
+        run_reference_triton_arm(args, wl)
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the sparse-prefill kernels have no CPU fallback")
