@@ -40,7 +40,7 @@ from shareprefill_b200.workloads import WORKLOADS, AttentionWorkload, make_qkv, 
 
 STAGES = ["pool", "profile", "select", "attention", "pivot_update"]
 # kernels launched per layer by each stage (this library's own kernels)
-LAUNCHES_PER_LAYER = {"pool": 1, "profile": 3, "select": 7, "attention": 1, "pivot_update": 2}
+LAUNCHES_PER_LAYER = {"pool": 1, "profile": 3, "select": 7, "attention": 2, "pivot_update": 2, "block_count": 1}
 DISTINCT_LAYER_INPUTS = 4   # host/device inputs are drawn for this many layers and cycled
 # DRAM bytes (read + write) of ONE launch of the block-sparse attention kernel, from ncu captures of
 # these workloads on one GPU (profiles/sparse_attn_tc5_cfg1_and_cfg2.md); None where not captured
@@ -330,6 +330,11 @@ def run_gpu_arm(args, wl):
     for _ in range(args.warmup):
         step_resident()
     barrier()
+    # host time to ISSUE one step (no synchronisation): tells whether a step is launch bound
+    h0 = time.perf_counter()
+    step_resident()
+    host_issue_ms = (time.perf_counter() - h0) * 1e3
+    barrier()
     sampler = ClockSampler(local)
     sampler.start()
     sharing.on_stage = on_stage
@@ -455,7 +460,7 @@ def run_gpu_arm(args, wl):
         "data": "synthetic", "config": config_dict(wl, world),
         "effective_tflops": flops_all / (ms_step / 1e3) / 1e12,
         "visited_block_fraction": blocks_all / (tri * wl.num_q_heads * L),
-        "stage_ms_rank0": stage_ms,
+        "stage_ms_rank0": stage_ms, "host_issue_ms_per_step": host_issue_ms,
         "roofline": {"kernel": "block-sparse attention", "bound": "tensor", "achieved": achieved_tf,
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved_tf / peaks["tflops"],
                      "traffic": ATTENTION_DRAM_BYTES_PER_LAUNCH.get((wl.name, wl.seq_len, wl.q_gain)) if world == 1 else None,

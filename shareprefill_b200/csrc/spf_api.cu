@@ -259,6 +259,7 @@ int spf_sparse_attention(const void* q, int64_t q_stride_n, int64_t q_stride_h, 
   p.nb = ceil_div(n_tokens, block_size); p.nbw = (p.nb + 31) / 32;
   p.scale_log2 = static_cast<float>(softmax_scale * 1.4426950408889634);
   p.pivot_only = 0;
+  p.n_slots = with_state ? n_slots : 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // block_size = head_dim = 128 runs on the tcgen05 kernel; SPF_ATTENTION_KERNEL=generic (a test
   // hook) keeps the mma.sync kernel, which also serves every other supported shape

@@ -61,8 +61,20 @@ __global__ void __launch_bounds__(BS * 2) sparse_attn_generic_kernel(const AttnP
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // heavy (late) query blocks first
-  const int r = p.nb - 1 - static_cast<int>(blockIdx.x / p.n_q_heads);
-  const int h = static_cast<int>(blockIdx.x % p.n_q_heads);
+  int r, h;
+  if (!p.pivot_only) {
+    r = p.nb - 1 - static_cast<int>(blockIdx.x / p.n_q_heads);
+    h = static_cast<int>(blockIdx.x % p.n_q_heads);
+  } else {
+    // pivot-only pass: one CTA per (query block, shared cluster); the cluster's pivot of this layer,
+    // if any, is the head flagged PIVOT whose slot matches
+    r = p.nb - 1 - static_cast<int>(blockIdx.x / p.n_slots);
+    const int slot = static_cast<int>(blockIdx.x % p.n_slots);
+    h = -1;
+    for (int i = 0; i < p.n_q_heads; ++i)
+      if ((p.head_flags[i] & SPF_HEAD_PIVOT) && p.slot_of_head[i] == slot) { h = i; break; }
+    if (h < 0) return;
+  }
   const bool is_pivot = p.head_flags != nullptr && p.pivot_attn != nullptr &&
                         (p.head_flags[h] & SPF_HEAD_PIVOT) && p.slot_of_head[h] >= 0;
   if (p.pivot_only && !is_pivot) return;
@@ -287,7 +299,8 @@ static int launch_generic(const AttnParams& p, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
   }
-  const unsigned grid = static_cast<unsigned>(p.nb) * static_cast<unsigned>(p.n_q_heads);
+  const unsigned grid = static_cast<unsigned>(p.nb) *
+                        static_cast<unsigned>(p.pivot_only ? p.n_slots : p.n_q_heads);
   kern<<<grid, NT, SMEM, st>>>(p);
   return check_launch();
 }

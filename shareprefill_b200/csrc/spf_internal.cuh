@@ -17,6 +17,7 @@ struct AttnParams {
   int n_tokens, n_q_heads, group, nb, nbw;
   float scale_log2;        // softmax_scale * log2(e)
   int pivot_only;          // 1: only pivot heads run, only their block-mass matrix is written
+  int n_slots;             // shared clusters (grid of the pivot-only pass is nb x n_slots)
 };
 
 struct EstParams {

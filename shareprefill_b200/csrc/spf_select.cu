@@ -50,13 +50,26 @@ __global__ void __launch_bounds__(256) pooled_last_row_kernel(const LastRowParam
   const int kvh = h / (p.n_q_heads / p.n_kv_heads);
   const int rows = min(p.block_size, p.n_tokens);
   const int q0 = p.n_tokens - rows;
-  if (tid < p.head_dim) {
-    float acc = 0.f;
-    for (int i = 0; i < rows; ++i) {
-      const float x = __bfloat162float(p.q[int64_t(q0 + i) * p.q_sn + int64_t(h) * p.q_sh + tid]);
-      acc += bf16_round(x / p.sqrt_d);
+  // mean over the last `rows` queries of bf16(q / sqrt(D)): warp w takes rows w, w+8, ...; a lane
+  // owns head_dim/32 consecutive elements of a row (coalesced), four rows in flight
+  {
+    const int per = p.head_dim >> 5;   // 2 or 4
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const __nv_bfloat16* base = p.q + int64_t(q0) * p.q_sn + int64_t(h) * p.q_sh + lane * per;
+    for (int i = warp; i < rows; i += 8) {
+      const __nv_bfloat16* rp = base + int64_t(i) * p.q_sn;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (e < per) acc[e] += bf16_round(__bfloat162float(rp[e]) / p.sqrt_d);
     }
-    qm[tid] = bf16_round(acc / static_cast<float>(rows));
+    float* part = dyn;                 // [8 warps][head_dim] scratch, before dyn holds the logits
+    for (int e = 0; e < per; ++e) part[warp * p.head_dim + lane * per + e] = acc[e];
+    __syncthreads();
+    if (tid < p.head_dim) {
+      float t = 0.f;
+      for (int w = 0; w < 8; ++w) t += part[w * p.head_dim + tid];
+      qm[tid] = bf16_round(t / static_cast<float>(rows));
+    }
   }
   __syncthreads();
   float lmax = -INFINITY;
@@ -415,7 +428,8 @@ int launch_budgets(const BudgetParams& p, cudaStream_t st) {
   return check_launch();
 }
 int launch_last_row(const LastRowParams& p, cudaStream_t st) {
-  pooled_last_row_kernel<<<p.n_q_heads, 256, p.nb * sizeof(float), st>>>(p);
+  const size_t dyn_floats = static_cast<size_t>(p.nb > 8 * p.head_dim ? p.nb : 8 * p.head_dim);
+  pooled_last_row_kernel<<<p.n_q_heads, 256, dyn_floats * sizeof(float), st>>>(p);
   return check_launch();
 }
 int launch_classify(const ClassifyParams& p, int n_heads, cudaStream_t st) {
