@@ -39,8 +39,6 @@ sys.path.insert(0, ROOT)
 from shareprefill_b200.workloads import WORKLOADS, AttentionWorkload, make_qkv, synthetic_lookup  # noqa: E402
 
 STAGES = ["pool", "profile", "select", "attention", "pivot_update"]
-# kernels launched per layer by each stage (this library's own kernels)
-LAUNCHES_PER_LAYER = {"pool": 1, "profile": 3, "select": 7, "attention": 2, "pivot_update": 2, "block_count": 1}
 DISTINCT_LAYER_INPUTS = 4   # host/device inputs are drawn for this many layers and cycled
 # DRAM bytes (read + write) of ONE launch of the block-sparse attention kernel, from ncu captures of
 # these workloads on one GPU (profiles/sparse_attn_tc5_cfg1_and_cfg2.md); None where not captured
@@ -339,12 +337,14 @@ def run_gpu_arm(args, wl):
     sampler.start()
     sharing.on_stage = on_stage
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = native.LAUNCH_COUNT
     t_begin.record()
     all_marks = []
     for _ in range(args.steps):
         m, visited = step_resident(record=True)
         all_marks.append(m)
     t_end.record()
+    launches_timed = native.LAUNCH_COUNT - launches_before
     barrier()
     clocks = sampler.stop()
     sharing.on_stage = None
@@ -452,7 +452,6 @@ def run_gpu_arm(args, wl):
         c = cpu_sample(wl)
         cpu = {"value": c["ms_per_step"], "unit": "ms", "cores": torch.get_num_threads(), "kind": "port",
                "sample": c["sample"]}
-    launches = L * sum(LAUNCHES_PER_LAYER.values()) + 1
     line = {
         "metric": "sparse_prefill_attention_ms_per_forward", "value": ms_step, "unit": "ms",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -472,7 +471,7 @@ def run_gpu_arm(args, wl):
                           "traffic_unit": "bytes per launch (ncu dram read+write)", "of": peaks["source"]},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
-        "gpu_launches": launches * args.steps,
+        "gpu_launches": launches_timed,
         "clocks": clocks,
     }
     print(json.dumps(line))

@@ -34,8 +34,9 @@ def sparse_prefill_attention(sharing, q, k, v, layer_idx: int, num_heads: int, c
         math.ceil(min_budget / block_size), math.ceil(max_budget / block_size),
         config.pattern_threshold, config.similarity_threshold, config.fallback_threshold,
         config.queryaware_threshold, False)
-    out = native.sparse_attention(q, k, v, pat.bitmap, block_size, scale, pat.flags, pat.slot_of_head,
-                                  sharing.state)
+    # layers without a head in a shared cluster cannot elect a pivot: no block-mass pass for them
+    state = sharing.state if pat.info.get("can_share", True) else None
+    out = native.sparse_attention(q, k, v, pat.bitmap, block_size, scale, pat.flags, pat.slot_of_head, state)
     sharing._mark("attention")
     sharing.update_pivotal_attns(layer_idx, None, use_dense, config.pattern_threshold)
     return out, pat

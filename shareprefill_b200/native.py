@@ -20,6 +20,13 @@ HEAD_PIVOT = 2
 HEAD_SHARED = 4
 
 _lib = None
+# kernels of this library launched so far by this process (counted per wrapper call)
+LAUNCH_COUNT = 0
+
+
+def _launched(n: int):
+    global LAUNCH_COUNT
+    LAUNCH_COUNT += n
 
 _P, _I, _L, _D = C.c_void_p, C.c_int, C.c_int64, C.c_double
 
@@ -127,6 +134,7 @@ def pool_qk(q: Optional[torch.Tensor], k: Optional[torch.Tensor], block_size: in
         avg_k = torch.empty(nb, hk, d, dtype=torch.bfloat16, device=k.device)
     _check(lib.spf_pool_qk(qp[0], qp[1], qp[2], kp[0], kp[1], kp[2], n, hq, hk, d, block_size,
                            _ptr(avg_q), _ptr(avg_k), _stream()), "spf_pool_qk")
+    _launched(1)
     return avg_q, avg_k
 
 
@@ -143,6 +151,7 @@ def lastblock_profile(q, k, block_size: int, scratch: Optional[torch.Tensor] = N
                                      block_size, vertical.data_ptr(), slash.data_ptr(),
                                      scratch.data_ptr(), scratch.numel(), _stream()),
            "spf_lastblock_profile")
+    _launched(3)
     return vertical, slash
 
 
@@ -159,6 +168,7 @@ def profile_budgets(vertical, slash, block_size, pattern_threshold, min_blocks, 
                                    float(pattern_threshold), int(min_blocks), int(min(max_blocks, 2**31 - 1)),
                                    nv.data_ptr(), ns.data_ptr(), vpool.data_ptr(), spool.data_ptr(),
                                    _stream()), "spf_profile_budgets")
+    _launched(1)
     return nv, ns, vpool, spool
 
 
@@ -170,6 +180,7 @@ def pooled_last_row(q, avg_k, block_size):
     qp = _nhd(q)
     _check(lib.spf_pooled_last_row(qp[0], qp[1], qp[2], avg_k.data_ptr(), n, h, avg_k.shape[1], d,
                                    block_size, out.data_ptr(), _stream()), "spf_pooled_last_row")
+    _launched(1)
     return out
 
 
@@ -198,6 +209,7 @@ class SharingStateBuffer:
     def reset(self):
         _check(load().spf_sharing_state_reset(self.ptr, self.n_slots, self.nb, _stream()),
                "spf_sharing_state_reset")
+        _launched(1)
 
     def field(self, name: str) -> torch.Tensor:
         """A typed view of one state array (for tests and cross-GPU exchange)."""
@@ -227,6 +239,7 @@ def classify_heads(avg_qk, vpool, spool, slot_of_head, state: SharingStateBuffer
                                   slot_of_head.data_ptr(), state.ptr, state.n_slots, h, nb,
                                   out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(), _stream()),
            "spf_classify_heads")
+    _launched(1)
     return out[0], out[1], out[2]
 
 
@@ -241,6 +254,7 @@ def elect_and_share(jsd_qa_all, slot_all, head_offset, jsd_v, jsd_s, vpool, spoo
                                    float(queryaware_threshold), float(similarity_threshold),
                                    float(fallback_threshold), int(min_blocks), nv.data_ptr(), ns.data_ptr(),
                                    flags.data_ptr(), _stream()), "spf_elect_and_share")
+    _launched(1)
     return flags
 
 
@@ -252,6 +266,7 @@ def build_vs_bitmap(vpool, spool, nv, ns, flags, slot_of_head, state, bitmap=Non
     _check(lib.spf_build_vs_bitmap(vpool.data_ptr(), spool.data_ptr(), nv.data_ptr(), ns.data_ptr(),
                                    flags.data_ptr(), slot_of_head.data_ptr(), state.ptr, state.n_slots,
                                    h, nb, bitmap.data_ptr(), _stream()), "spf_build_vs_bitmap")
+    _launched(1)
     return bitmap
 
 
@@ -262,6 +277,7 @@ def query_aware_scores(avg_q, avg_k, flags, scores=None):
         scores = torch.zeros(h, nb, nb, dtype=torch.float32, device=avg_q.device)
     _check(lib.spf_query_aware_scores(avg_q.data_ptr(), avg_k.data_ptr(), _ptr(flags), h, avg_k.shape[1],
                                       d, nb, scores.data_ptr(), _stream()), "spf_query_aware_scores")
+    _launched(1)
     return scores
 
 
@@ -270,6 +286,7 @@ def query_aware_select(scores, flags, pattern_threshold, bitmap):
     h, nb, _ = scores.shape
     _check(lib.spf_query_aware_select(scores.data_ptr(), _ptr(flags), h, nb, float(pattern_threshold),
                                       bitmap.data_ptr(), _stream()), "spf_query_aware_select")
+    _launched(1)
     return bitmap
 
 
@@ -280,6 +297,7 @@ def bitmap_row_counts(bitmap):
     tot = torch.empty(h, dtype=torch.int64, device=bitmap.device)
     _check(lib.spf_bitmap_row_counts(bitmap.data_ptr(), h, nb, rows.data_ptr(), tot.data_ptr(), _stream()),
            "spf_bitmap_row_counts")
+    _launched(1)
     return rows, tot
 
 
@@ -296,6 +314,8 @@ def sparse_attention(q, k, v, bitmap, block_size, softmax_scale, flags=None, slo
                                     None if state is None else state.ptr,
                                     0 if state is None else state.n_slots, out.data_ptr(), _stream()),
            "spf_sparse_attention")
+    # the tcgen05 kernel is followed by a pivot-only pass of the generic kernel when state is given
+    _launched(2 if (state is not None and state.n_slots > 0 and block_size == 128 and d == 128) else 1)
     return out
 
 
@@ -304,6 +324,7 @@ def update_pivots(flags, slot_of_head, state: SharingStateBuffer, pattern_thresh
     _check(lib.spf_update_pivots(flags.data_ptr(), slot_of_head.data_ptr(), state.ptr, state.n_slots,
                                  flags.numel(), state.nb, float(pattern_threshold), _stream()),
            "spf_update_pivots")
+    _launched(2)
 
 
 # ---------------------------------------------------------------------------- format helpers

@@ -72,6 +72,7 @@ class AttentionSharing:
         self.head_range = head_range
         self.exchange = exchange
         self._slot_tables: Dict[Tuple[int, int, str], torch.Tensor] = {}
+        self._layer_shares: Dict[Tuple[int, int], bool] = {}
         self._state: Optional[native.SharingStateBuffer] = None
         self._needs_reset = True
         self.last_pattern: Optional[BlockPattern] = None
@@ -104,7 +105,13 @@ class AttentionSharing:
                 slots.append(self._slot_index.get(cid, -1))
             t = torch.tensor(slots, dtype=torch.int32, device=device)
             self._slot_tables[key] = t
+            self._layer_shares[(int(layer), num_heads)] = any(x >= 0 for x in slots)
         return t
+
+    def layer_can_share(self, layer: int, num_heads: int) -> bool:
+        """Does any head of this layer belong to a shared cluster?  Known from the lookup alone, so
+        the host may skip the pivot passes and the pivot exchange of layers where it is False."""
+        return self._layer_shares.get((int(layer), num_heads), True)
 
     # ---- state
     def reset_state(self):
@@ -191,7 +198,7 @@ class AttentionSharing:
                                                       min_budget, max_blocks)
         avg_qk = si["avg_qk"] if "avg_qk" in si else native.pooled_last_row(q, avg_k, block_size)
         jsd_qa, jsd_v, jsd_s = native.classify_heads(avg_qk, vpool, spool, slot_local, state)
-        return dict(layer=layer_idx, nb=nb, h0=h0, state=state, slot_all=slot_all, slot_local=slot_local,
+        return dict(layer=layer_idx, nb=nb, h0=h0, state=state, num_heads=num_heads, slot_all=slot_all, slot_local=slot_local,
                     avg_q=avg_q, avg_k=avg_k, vertical=vertical, slash=slash, nv=nv, ns=ns, vpool=vpool,
                     spool=spool, avg_qk=avg_qk, jsd_qa=jsd_qa, jsd_v=jsd_v, jsd_s=jsd_s,
                     min_blocks=min_budget, pattern_threshold=pattern_threshold,
@@ -212,8 +219,9 @@ class AttentionSharing:
             scores = native.query_aware_scores(ctx["avg_q"], ctx["avg_k"], flags)
         native.query_aware_select(scores, flags, ctx["pattern_threshold"], bitmap)
         pat = BlockPattern(bitmap, flags, ctx["slot_local"], ctx["nb"], nv, ns,
-                           info={k_: ctx[k_] for k_ in ("vertical", "slash", "vpool", "spool", "avg_qk",
-                                                        "avg_k", "avg_q", "jsd_qa", "jsd_v", "jsd_s")})
+                           info={"can_share": self.layer_can_share(ctx["layer"], ctx["num_heads"]),
+                                 **{k_: ctx[k_] for k_ in ("vertical", "slash", "vpool", "spool", "avg_qk",
+                                                        "avg_k", "avg_q", "jsd_qa", "jsd_v", "jsd_s")}})
         self.last_pattern = pat
         self._mark("select")
         return pat, pat.use_dense
@@ -224,7 +232,7 @@ class AttentionSharing:
         state by the attention kernel; ``avg_attn`` / ``use_dense`` are accepted for signature
         compatibility and ignored."""
         pat = self.last_pattern
-        if pat is not None and self._state is not None and self.slot_ids:
+        if pat is not None and self._state is not None and self.slot_ids and pat.info.get("can_share", True):
             native.update_pivots(pat.flags, pat.slot_of_head, self._state, pattern_threshold)
             if self.exchange is not None:
                 self.exchange.share_new_pivots(self, layer_idx)
