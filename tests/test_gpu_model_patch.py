@@ -48,3 +48,10 @@ def test_generate_runs_prefill_then_decode(tmp_path):
     with torch.no_grad():
         out = model.generate(ids, max_new_tokens=4, do_sample=False)
     assert out.shape == (1, 304)
+
+
+def test_latency_driver_runs_on_a_tiny_model():
+    from shareprefill_b200 import latency
+    res = latency.main(["--model", "tiny", "--lengths", "512,1000", "--num-exp", "1",
+                        "--cfg", "block_size=64,min_budget=128,pattern_threshold=0.95"])
+    assert [r["length"] for r in res] == [512, 1000] and all(r["seconds"] > 0 for r in res)
