@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout (it cannot travel):
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <path to the reference checkout>
 
 The reference's ``AttentionSharing.get_active_blocks`` / ``update_pivotal_attns``
 (shareprefill/attn/attention_sharing.py:94-366) and their helpers
@@ -227,7 +227,7 @@ def helper_vectors(utils):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path to the reference checkout")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     sys.path.insert(0, args.reference)

@@ -9,9 +9,11 @@ them unmodified - from an offline install of the reference under baseline/_ref, 
 
 - on seeded inputs and stores the outputs:
 
-    python tests/golden/make_golden_triton.py --out tests/golden/triton_kernels.npz
+    python tests/golden/make_golden_triton.py --out triton_kernels_full.npz
 
-Inputs are regenerated from the seeds by the tests (torch CPU generator), outputs are stored.
+Inputs are regenerated from the seeds by the tests (torch CPU generator), outputs are stored.  The
+committed tests/golden/triton_kernels.npz is that file with the largest case's output thinned to
+every eighth row (key ``c128_o_bits_rows8``) to keep the fixture small.
 """
 import argparse
 import os
@@ -53,7 +55,7 @@ def case_inputs(name):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "triton_kernels.npz"))
+    ap.add_argument("--out", default=os.path.join(HERE, "triton_kernels_full.npz"))
     ap.add_argument("--ref", default=os.path.join(ROOT, "baseline", "_ref"))
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
