@@ -217,6 +217,20 @@ int spf_sparse_attention(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                          const int32_t* head_flags, const int32_t* slot_of_head, void* state,
                          int n_slots, void* out, void* stream);
 
+/* ---------------------------------------------------------------- decode step
+ * One query token per head against the KV cache (q_len == 1): dense softmax attention, the step
+ * the reference hands to flash_attn_func (attn/shareprefill_attn.py:146-153).
+ * q: bf16 [H][D] (head stride q_stride_h); k, v: bf16 [n_keys][Hkv][D] views; out: bf16 [H][D].
+ * scratch: spf_decode_scratch_bytes() bytes of split-K partials, overwritten.
+ */
+int64_t spf_decode_scratch_bytes(int n_keys, int n_q_heads, int head_dim);
+int spf_decode_attention(const void* q, int64_t q_stride_h,
+                         const void* k, int64_t k_stride_n, int64_t k_stride_h,
+                         const void* v, int64_t v_stride_n, int64_t v_stride_h,
+                         int n_keys, int n_q_heads, int n_kv_heads, int head_dim,
+                         double softmax_scale, void* out, void* scratch, int64_t scratch_bytes,
+                         void* stream);
+
 /* Number of bounded device-side waits that gave up since the library was loaded (0 in a
  * healthy run).  The tcgen05 kernel never spins without a limit: a wait that runs out makes
  * its CTA drain and return, and is counted here.  Synchronises the device. */

@@ -476,6 +476,19 @@ def masked_dense_attention(q, k, v, block_sets, bs: int, scale: Optional[float] 
     return o
 
 
+def decode_attention(q, k, v, scale: Optional[float] = None):
+    """One decode step: q ``[H,D]`` against the whole cache k/v ``[Nk,Hkv,D]``, fp32 softmax.
+    The reference hands this step to flash_attn_func (attn/shareprefill_attn.py:146-153)."""
+    h, d = q.shape
+    g = h // k.shape[1]
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    kf = k.float().repeat_interleave(g, 1)
+    vf = v.float().repeat_interleave(g, 1)
+    s = torch.einsum("hd,nhd->hn", q.float(), kf) * scale
+    return torch.einsum("hn,nhd->hd", torch.softmax(s, dim=-1), vf)
+
+
 def sparse_prefill_layer(state: SharingOracle, q, k, v, layer: int, *, block_size=128,
                          min_budget=1024, max_budget=None, pattern_threshold=0.9,
                          similarity_threshold=0.5, fallback_threshold=0.9,

@@ -67,8 +67,16 @@ def shareprefill_attention_core(module, query_states, key_states, value_states, 
             attn_weights = dense_avg_attn(module.attention_sharing, pat, num_heads)
         return out[None], attn_weights
 
-    # decode step: dense attention over the cache; a library call in the reference as well
-    # (flash_attn_func, attn/shareprefill_attn.py:146-153)
+    # decode step (one query token): dense attention over the cache with the split-K decode kernel;
+    # the reference calls flash_attn_func here (attn/shareprefill_attn.py:146-153)
+    if (query_states.is_cuda and query_states.dtype == torch.bfloat16 and not module.training
+            and head_dim in (64, 128)):
+        outs = []
+        for b in range(bsz):
+            outs.append(native.decode_attention(query_states[b, :, 0, :], _token_major(key_states[b]),
+                                                _token_major(value_states[b]), softmax_scale))
+        return torch.stack(outs)[:, None], None
+    # anything else (training-time dropout, other dtypes): torch's dense attention
     groups = num_heads // key_states.shape[1]
     out = torch.nn.functional.scaled_dot_product_attention(
         query_states, key_states, value_states,

@@ -107,6 +107,17 @@ struct PivotParams {
   StateView st; int n_slots, nb, nbw; float thr;
 };
 
+struct DecodeParams {
+  const __nv_bfloat16* q; int64_t q_sh;
+  const __nv_bfloat16* k; int64_t k_sn, k_sh;
+  const __nv_bfloat16* v; int64_t v_sn, v_sh;
+  __nv_bfloat16* out;      // [H][D]
+  float* scratch;          // [H][splits][D + 2]
+  int n_keys, n_q_heads, group, splits;
+  float scale_log2;
+};
+
+int decode_attention(const DecodeParams& p, int head_dim, cudaStream_t st);
 int sparse_attention_generic(const AttnParams& p, int block_size, int head_dim, cudaStream_t st);
 int sparse_attention_tc5(const AttnParams& p, int n_kv_heads, cudaStream_t st);
 unsigned int tc5_timeout_count();

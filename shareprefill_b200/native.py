@@ -54,6 +54,8 @@ SIGNATURES = {
     "spf_sparse_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P,
                                   _P, _I, _P, _P]),
     "spf_device_timeouts": (_I, []),
+    "spf_decode_scratch_bytes": (_L, [_I, _I, _I]),
+    "spf_decode_attention": (_I, [_P, _L, _P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _D, _P, _P, _L, _P]),
     "spf_update_pivots": (_I, [_P, _P, _P, _I, _I, _I, _D, _P]),
 }
 
@@ -316,6 +318,26 @@ def sparse_attention(q, k, v, bitmap, block_size, softmax_scale, flags=None, slo
            "spf_sparse_attention")
     # the tcgen05 kernel is followed by a pivot-only pass of the generic kernel when state is given
     _launched(2 if (state is not None and state.n_slots > 0 and block_size == 128 and d == 128) else 1)
+    return out
+
+
+def decode_attention(q, k, v, softmax_scale, out=None):
+    """q ``[H,D]``, k/v ``[Nk,Hkv,D]`` views -> ``[H,D]`` (one decode step, dense attention)."""
+    lib = load()
+    h, d = q.shape
+    nk = k.shape[0]
+    if q.dtype != torch.bfloat16 or q.stride(1) != 1:
+        raise SpfError("decode query must be a bfloat16 [H,D] view with contiguous D")
+    if k.shape != v.shape or k.shape[2] != d or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise SpfError(f"decode cache shapes {tuple(k.shape)}/{tuple(v.shape)} do not match query {tuple(q.shape)}")
+    if out is None:
+        out = torch.empty(h, d, dtype=torch.bfloat16, device=q.device)
+    scratch = torch.empty(lib.spf_decode_scratch_bytes(nk, h, d), dtype=torch.uint8, device=q.device)
+    kp, vp = _nhd(k), _nhd(v)
+    _check(lib.spf_decode_attention(q.data_ptr(), q.stride(0), kp[0], kp[1], kp[2], vp[0], vp[1], vp[2], nk, h,
+                                    k.shape[1], d, float(softmax_scale), out.data_ptr(), scratch.data_ptr(),
+                                    scratch.numel(), _stream()), "spf_decode_attention")
+    _launched(2)
     return out
 
 
