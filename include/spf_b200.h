@@ -223,7 +223,7 @@ int spf_sparse_attention(const void* q, int64_t q_stride_n, int64_t q_stride_h,
  * q: bf16 [H][D] (head stride q_stride_h); k, v: bf16 [n_keys][Hkv][D] views; out: bf16 [H][D].
  * scratch: spf_decode_scratch_bytes() bytes of split-K partials, overwritten.
  */
-int64_t spf_decode_scratch_bytes(int n_keys, int n_q_heads, int head_dim);
+int64_t spf_decode_scratch_bytes(int n_keys, int n_q_heads, int n_kv_heads, int head_dim);
 int spf_decode_attention(const void* q, int64_t q_stride_h,
                          const void* k, int64_t k_stride_n, int64_t k_stride_h,
                          const void* v, int64_t v_stride_n, int64_t v_stride_h,

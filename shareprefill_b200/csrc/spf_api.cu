@@ -277,18 +277,23 @@ int spf_sparse_attention(const void* q, int64_t q_stride_n, int64_t q_stride_h, 
   return sparse_attention_generic(p, block_size, head_dim, st);
 }
 
-static int decode_splits(int n_keys, int n_q_heads) {
-  int s = (148 * 4) / (n_q_heads > 0 ? n_q_heads : 1);
-  const int by_len = (n_keys + 255) / 256;
-  if (s > by_len) s = by_len;
-  if (s < 1) s = 1;
+// Token splits of the decode pass: about two CTAs per SM over (splits x CTA rows), at least four
+// 16-token tiles per split, every split non-empty.
+static int decode_splits(int n_keys, int n_q_heads, int n_kv_heads) {
+  const int rows = (n_q_heads / n_kv_heads <= 16) ? n_kv_heads : n_q_heads;   // CTA rows of the grid
+  const int tiles = (n_keys + 15) / 16;
+  int s = (2 * 148 + rows - 1) / rows;
+  if (s > (tiles + 3) / 4) s = (tiles + 3) / 4;
   if (s > 256) s = 256;
-  return s;
+  if (s < 1) s = 1;
+  const int per = (tiles + s - 1) / s;
+  return (tiles + per - 1) / per;
 }
 
-int64_t spf_decode_scratch_bytes(int n_keys, int n_q_heads, int head_dim) {
-  if (n_keys <= 0 || n_q_heads <= 0 || !supported_head_dim(head_dim)) return 0;
-  return align256(int64_t(n_q_heads) * decode_splits(n_keys, n_q_heads) * (head_dim + 2) * 4);
+int64_t spf_decode_scratch_bytes(int n_keys, int n_q_heads, int n_kv_heads, int head_dim) {
+  if (n_keys <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads || !supported_head_dim(head_dim))
+    return 0;
+  return align256(int64_t(n_q_heads) * decode_splits(n_keys, n_q_heads, n_kv_heads) * (head_dim + 2) * 4);
 }
 
 int spf_decode_attention(const void* q, int64_t q_stride_h, const void* k, int64_t k_stride_n, int64_t k_stride_h,
@@ -302,14 +307,14 @@ int spf_decode_attention(const void* q, int64_t q_stride_h, const void* k, int64
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(scratch) ||
       q_stride_h % 8 || !strides_ok(k_stride_n, k_stride_h) || !strides_ok(v_stride_n, v_stride_h))
     return SPF_ERR_ALIGN;
-  if (scratch_bytes < spf_decode_scratch_bytes(n_keys, n_q_heads, head_dim)) return SPF_ERR_RANGE;
+  if (scratch_bytes < spf_decode_scratch_bytes(n_keys, n_q_heads, n_kv_heads, head_dim)) return SPF_ERR_RANGE;
   DecodeParams p;
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_sh = q_stride_h;
   p.k = static_cast<const __nv_bfloat16*>(k); p.k_sn = k_stride_n; p.k_sh = k_stride_h;
   p.v = static_cast<const __nv_bfloat16*>(v); p.v_sn = v_stride_n; p.v_sh = v_stride_h;
   p.out = static_cast<__nv_bfloat16*>(out); p.scratch = static_cast<float*>(scratch);
   p.n_keys = n_keys; p.n_q_heads = n_q_heads; p.group = n_q_heads / n_kv_heads;
-  p.splits = decode_splits(n_keys, n_q_heads);
+  p.splits = decode_splits(n_keys, n_q_heads, n_kv_heads);
   p.scale_log2 = static_cast<float>(softmax_scale * 1.4426950408889634);
   return decode_attention(p, head_dim, static_cast<cudaStream_t>(stream));
 }

@@ -54,7 +54,7 @@ SIGNATURES = {
     "spf_sparse_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P,
                                   _P, _I, _P, _P]),
     "spf_device_timeouts": (_I, []),
-    "spf_decode_scratch_bytes": (_L, [_I, _I, _I]),
+    "spf_decode_scratch_bytes": (_L, [_I, _I, _I, _I]),
     "spf_decode_attention": (_I, [_P, _L, _P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _D, _P, _P, _L, _P]),
     "spf_update_pivots": (_I, [_P, _P, _P, _I, _I, _I, _D, _P]),
 }
@@ -332,7 +332,7 @@ def decode_attention(q, k, v, softmax_scale, out=None):
         raise SpfError(f"decode cache shapes {tuple(k.shape)}/{tuple(v.shape)} do not match query {tuple(q.shape)}")
     if out is None:
         out = torch.empty(h, d, dtype=torch.bfloat16, device=q.device)
-    scratch = torch.empty(lib.spf_decode_scratch_bytes(nk, h, d), dtype=torch.uint8, device=q.device)
+    scratch = torch.empty(lib.spf_decode_scratch_bytes(nk, h, k.shape[1], d), dtype=torch.uint8, device=q.device)
     kp, vp = _nhd(k), _nhd(v)
     _check(lib.spf_decode_attention(q.data_ptr(), q.stride(0), kp[0], kp[1], kp[2], vp[0], vp[1], vp[2], nk, h,
                                     k.shape[1], d, float(softmax_scale), out.data_ptr(), scratch.data_ptr(),

@@ -26,6 +26,7 @@ def _case(nk, h, hkv, d, seed, strided=False):
 @pytest.mark.parametrize("nk,h,hkv,d,strided", [
     (1, 32, 8, 128, False), (5, 32, 8, 128, False), (255, 32, 8, 128, True), (4097, 32, 8, 128, True),
     (70001, 32, 8, 128, False), (1000, 8, 2, 64, True), (33, 4, 4, 64, False), (3001, 64, 8, 128, False),
+    (777, 64, 4, 128, True), (2049, 32, 1, 128, False), (130, 48, 2, 64, False), (17, 1, 1, 128, False),
 ])
 def test_decode_matches_oracle(nk, h, hkv, d, strided):
     q, k, v = _case(nk, h, hkv, d, 1234 + nk, strided)
