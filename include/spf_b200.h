@@ -217,6 +217,22 @@ int spf_sparse_attention(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                          const int32_t* head_flags, const int32_t* slot_of_head, void* state,
                          int n_slots, void* out, void* stream);
 
+/* ---------------------------------------------------------------- head-sharded exchange
+ * With the heads of a layer split over several GPUs, the owner of a pivot elected in `layer` sends
+ * its summary to the other ranks (the reference keeps all heads in one process,
+ * attn/attention_sharing.py:94-103, so these have no counterpart there).  One int32 row of
+ * spf_pivot_summary_width(nb) words per slot: [flag][vs_ratio bits][vertical nb][slash nb]
+ * [pattern nb*ceil(nb/32)].  pack: rows of pivots elected in `layer` among heads
+ * [head_begin, head_end) are filled and flagged, the flag of every other row is cleared (payload
+ * untouched).  merge: `gathered` is [n_ranks][n_slots][width], as an all-gather of the packed rows
+ * leaves it; per slot the first flagged row is installed and the pattern marked ready.
+ */
+int64_t spf_pivot_summary_width(int nb);
+int spf_pack_pivot_summaries(void* state, int n_slots, int nb, int layer, int head_begin, int head_end,
+                             int32_t* packed, void* stream);
+int spf_merge_pivot_summaries(void* state, int n_slots, int nb, const int32_t* gathered, int n_ranks,
+                              void* stream);
+
 /* ---------------------------------------------------------------- decode step
  * One query token per head against the KV cache (q_len == 1): dense softmax attention, the step
  * the reference hands to flash_attn_func (attn/shareprefill_attn.py:146-153).

@@ -332,4 +332,26 @@ int spf_update_pivots(const int32_t* head_flags, const int32_t* slot_of_head, vo
   return launch_update_pivots(p, n_heads, static_cast<cudaStream_t>(stream));
 }
 
+int64_t spf_pivot_summary_width(int nb) {
+  if (nb <= 0 || nb > SPF_MAX_BLOCKS) return 0;
+  return 2 + 2 * int64_t(nb) + int64_t(nb) * ((nb + 31) / 32);
+}
+
+int spf_pack_pivot_summaries(void* state, int n_slots, int nb, int layer, int head_begin, int head_end,
+                             int32_t* packed, void* stream) {
+  if (!state || !packed) return SPF_ERR_NULL;
+  if (nb <= 0 || nb > SPF_MAX_BLOCKS || n_slots < 0 || head_begin < 0 || head_end < head_begin) return SPF_ERR_RANGE;
+  if (n_slots == 0) return SPF_OK;
+  return launch_pack_summaries(state, n_slots, nb, layer, head_begin, head_end, packed,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int spf_merge_pivot_summaries(void* state, int n_slots, int nb, const int32_t* gathered, int n_ranks,
+                              void* stream) {
+  if (!state || !gathered) return SPF_ERR_NULL;
+  if (nb <= 0 || nb > SPF_MAX_BLOCKS || n_slots < 0 || n_ranks <= 0) return SPF_ERR_RANGE;
+  if (n_slots == 0) return SPF_OK;
+  return launch_merge_summaries(state, n_slots, nb, gathered, n_ranks, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -134,5 +134,9 @@ int launch_row_counts(const uint32_t* bitmap, int n_heads, int nb, int32_t* row_
                       int64_t* head_totals, cudaStream_t st);
 int launch_update_pivots(const PivotParams& p, int n_heads, cudaStream_t st);
 int launch_state_reset(void* state, int n_slots, int nb, cudaStream_t st);
+int launch_pack_summaries(void* state, int n_slots, int nb, int layer, int h0, int h1, int32_t* out,
+                          cudaStream_t st);
+int launch_merge_summaries(void* state, int n_slots, int nb, const int32_t* gathered, int n_ranks,
+                           cudaStream_t st);
 
 }  // namespace spf

@@ -440,6 +440,65 @@ int launch_elect(const ElectParams& p, cudaStream_t st) {
   elect_and_share_kernel<<<1, 256, 0, st>>>(p);
   return check_launch();
 }
+// ---- pivot summaries for the head-sharded exchange.  One int32 row per slot:
+// [flag][vs_ratio bits][vertical nb][slash nb][pattern nb*nbw].  pack fills the rows of pivots elected
+// in `layer` among heads [h0, h1) and clears the flag of every other row (their payload is not
+// written and not read); merge installs, per slot, the first flagged row among the ranks.
+constexpr int SUMMARY_CHUNKS = 8;
+
+__device__ __forceinline__ void copy_words(int32_t* dst, const int32_t* src, int n) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n; i += SUMMARY_CHUNKS * blockDim.x) dst[i] = src[i];
+}
+
+__global__ void __launch_bounds__(256) pack_summaries_kernel(StateView st, int nb, int nbw, int layer, int h0,
+                                                            int h1, int32_t* out) {
+  const int s = blockIdx.x;
+  const int64_t width = 2 + 2 * int64_t(nb) + int64_t(nb) * nbw;
+  int32_t* row = out + s * width;
+  const int ph = st.pivot_head[s];
+  const bool mine = st.pivot_layer[s] == layer && ph >= h0 && ph < h1;
+  if (blockIdx.y == 0 && threadIdx.x == 0) {
+    row[0] = mine ? 1 : 0;
+    if (mine) row[1] = __float_as_int(st.vs_ratio[s]);
+  }
+  if (!mine) return;
+  copy_words(row + 2, reinterpret_cast<const int32_t*>(st.pivot_vertical + int64_t(s) * nb), nb);
+  copy_words(row + 2 + nb, reinterpret_cast<const int32_t*>(st.pivot_slash + int64_t(s) * nb), nb);
+  copy_words(row + 2 + 2 * nb, reinterpret_cast<const int32_t*>(st.pattern + int64_t(s) * nb * nbw), nb * nbw);
+}
+
+__global__ void __launch_bounds__(256) merge_summaries_kernel(StateView st, int n_slots, int nb, int nbw,
+                                                             const int32_t* gathered, int n_ranks) {
+  const int s = blockIdx.x;
+  const int64_t width = 2 + 2 * int64_t(nb) + int64_t(nb) * nbw;
+  const int32_t* row = nullptr;
+  for (int r = 0; r < n_ranks && !row; ++r) {
+    const int32_t* cand = gathered + (int64_t(r) * n_slots + s) * width;
+    if (cand[0] > 0) row = cand;
+  }
+  if (!row) return;
+  if (blockIdx.y == 0 && threadIdx.x == 0) {
+    st.vs_ratio[s] = __int_as_float(row[1]);
+    st.pattern_ready[s] = 1;
+  }
+  copy_words(reinterpret_cast<int32_t*>(st.pivot_vertical + int64_t(s) * nb), row + 2, nb);
+  copy_words(reinterpret_cast<int32_t*>(st.pivot_slash + int64_t(s) * nb), row + 2 + nb, nb);
+  copy_words(reinterpret_cast<int32_t*>(st.pattern + int64_t(s) * nb * nbw), row + 2 + 2 * nb, nb * nbw);
+}
+
+int launch_pack_summaries(void* state, int n_slots, int nb, int layer, int h0, int h1, int32_t* out,
+                          cudaStream_t st) {
+  pack_summaries_kernel<<<dim3(n_slots, SUMMARY_CHUNKS), 256, 0, st>>>(state_view(state, n_slots, nb), nb,
+                                                                      (nb + 31) / 32, layer, h0, h1, out);
+  return check_launch();
+}
+int launch_merge_summaries(void* state, int n_slots, int nb, const int32_t* gathered, int n_ranks,
+                           cudaStream_t st) {
+  merge_summaries_kernel<<<dim3(n_slots, SUMMARY_CHUNKS), 256, 0, st>>>(state_view(state, n_slots, nb), n_slots,
+                                                                       nb, (nb + 31) / 32, gathered, n_ranks);
+  return check_launch();
+}
+
 int launch_vs_bitmap(const VsParams& p, int n_heads, cudaStream_t st) {
   const size_t smem = size_t(p.nb) * 8 + size_t(p.nbw) * 8;
   if (smem > 48 * 1024) {

@@ -54,6 +54,9 @@ SIGNATURES = {
     "spf_sparse_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P,
                                   _P, _I, _P, _P]),
     "spf_device_timeouts": (_I, []),
+    "spf_pivot_summary_width": (_L, [_I]),
+    "spf_pack_pivot_summaries": (_I, [_P, _I, _I, _I, _I, _I, _P, _P]),
+    "spf_merge_pivot_summaries": (_I, [_P, _I, _I, _P, _I, _P]),
     "spf_decode_scratch_bytes": (_L, [_I, _I, _I, _I]),
     "spf_decode_attention": (_I, [_P, _L, _P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _D, _P, _P, _L, _P]),
     "spf_update_pivots": (_I, [_P, _P, _P, _I, _I, _I, _D, _P]),
@@ -347,6 +350,27 @@ def update_pivots(flags, slot_of_head, state: SharingStateBuffer, pattern_thresh
                                  flags.numel(), state.nb, float(pattern_threshold), _stream()),
            "spf_update_pivots")
     _launched(2)
+
+
+def pack_pivot_summaries(state: SharingStateBuffer, layer: int, h0: int, h1: int, out=None) -> torch.Tensor:
+    """int32 ``[S, width]`` rows of the pivots elected in ``layer`` among heads ``[h0, h1)``."""
+    lib = load()
+    width = lib.spf_pivot_summary_width(state.nb)
+    if out is None:
+        out = torch.empty(state.n_slots, width, dtype=torch.int32, device=state.buf.device)
+    _check(lib.spf_pack_pivot_summaries(state.ptr, state.n_slots, state.nb, int(layer), int(h0), int(h1),
+                                        out.data_ptr(), _stream()), "spf_pack_pivot_summaries")
+    _launched(1)
+    return out
+
+
+def merge_pivot_summaries(state: SharingStateBuffer, gathered: torch.Tensor) -> None:
+    """Install flagged rows of ``gathered [ranks, S, width]`` into the state."""
+    lib = load()
+    assert gathered.dtype == torch.int32 and gathered.is_contiguous()
+    _check(lib.spf_merge_pivot_summaries(state.ptr, state.n_slots, state.nb, gathered.data_ptr(),
+                                         gathered.shape[0], _stream()), "spf_merge_pivot_summaries")
+    _launched(1)
 
 
 # ---------------------------------------------------------------------------- format helpers

@@ -65,6 +65,7 @@ class HeadShardExchange:
         self.h0, self.h1 = head_begin, head_end
         self.group = group
         self.world = dist.get_world_size(group)
+        self._buffers = None
 
     def gather_heads(self, local: torch.Tensor) -> torch.Tensor:
         """All ranks' per-head values in global head order (equal shard sizes)."""
@@ -76,6 +77,22 @@ class HeadShardExchange:
         st = sharing.state
         if st is None or st.n_slots == 0:
             return
+        from . import native
+        if isinstance(st, native.SharingStateBuffer):
+            # device state: one pack kernel, the all-gather, one merge kernel; buffers are reused
+            key = (st.n_slots, st.nb, st.buf.device)
+            if self._buffers is None or self._buffers[0] != key:
+                width = native.load().spf_pivot_summary_width(st.nb)
+                packed = torch.empty(st.n_slots, width, dtype=torch.int32, device=st.buf.device)
+                flat = torch.empty(self.world, st.n_slots, width, dtype=torch.int32, device=st.buf.device)
+                self._buffers = (key, packed, flat)
+            _, packed, flat = self._buffers
+            native.pack_pivot_summaries(st, layer, self.h0, self.h1, out=packed)
+            dist.all_gather_into_tensor(flat.view(-1), packed.view(-1), group=self.group)
+            native.merge_pivot_summaries(st, flat)
+            return
+        # any other state object exposing field(): the same exchange in torch ops (tests of the
+        # exchange logic on CPU process groups)
         packed = pack_pivot_summaries(st, layer, self.h0, self.h1)
         flat = torch.empty(self.world * packed.numel(), dtype=packed.dtype, device=packed.device)
         dist.all_gather_into_tensor(flat, packed.reshape(-1), group=self.group)

@@ -16,8 +16,9 @@ from shareprefill_b200.sharing_state import AttentionSharing
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("exchange", ["kernels", "torch"])
 @pytest.mark.parametrize("name", ["peaky_share", "ragged_rope", "peaky_default"])
-def test_two_shards_equal_one(name, tmp_path):
+def test_two_shards_equal_one(name, exchange, tmp_path):
     dev = torch.device("cuda:0")
     gc = GoldenCase(name)
     wl = gc.wl
@@ -50,9 +51,18 @@ def test_two_shards_equal_one(name, tmp_path):
                                                 sp.flags, sp.slot_of_head, sh.state))
             sh.update_pivotal_attns(layer, None, sd, wl.pattern_threshold)
             pats.append(sp)
-        gathered = torch.stack([pack_pivot_summaries(sh.state, layer, s[0], s[1]) for s, sh in zip(shards, parts)])
-        for sh in parts:
-            merge_pivot_summaries(sh.state, gathered)
+        want = torch.stack([pack_pivot_summaries(sh.state, layer, s[0], s[1]) for s, sh in zip(shards, parts)])
+        if exchange == "kernels":   # the pack / merge kernels the NCCL path uses
+            gathered = torch.stack([native.pack_pivot_summaries(sh.state, layer, s[0], s[1])
+                                    for s, sh in zip(shards, parts)])
+            sent = want[:, :, 0] > 0
+            assert torch.equal(gathered[:, :, 0], want[:, :, 0]), "flags differ from the torch packing"
+            assert torch.equal(gathered[sent], want[sent]), "packed rows differ from the torch packing"
+            for sh in parts:
+                native.merge_pivot_summaries(sh.state, gathered)
+        else:
+            for sh in parts:
+                merge_pivot_summaries(sh.state, want)
         assert torch.equal(torch.cat([p.bitmap for p in pats]), pat.bitmap), f"layer {layer}: patterns differ"
         assert torch.equal(torch.cat([p.flags for p in pats]), pat.flags), f"layer {layer}: flags differ"
         assert torch.equal(torch.cat(outs, dim=1), out), f"layer {layer}: outputs differ"
