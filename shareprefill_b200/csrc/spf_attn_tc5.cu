@@ -7,10 +7,12 @@
 //   warp 0      TMA producer: Q tiles once, then K and V tiles of the union of both heads' bitmap
 //               rows through a 3-deep K ring and a 2-deep V ring (cp.async.bulk.tensor, 128-byte
 //               swizzle, no multicast)
-//   warp 1      MMA issuer: S_h = Q_h K^T (both operands in shared memory) and O_h += P_h V
-//               (P_h read from TMEM, V from shared memory) with tcgen05.mma, accumulators in TMEM;
-//               completion is signalled to mbarriers with tcgen05.commit
-//   warps 2-3   idle (they only complete the control warpgroup, which gives most of its registers
+//   warps 1, 2  MMA issuers: S_h = Q_h K^T (both operands in shared memory) and O_h += P_h V (P_h read
+//               from TMEM, V from shared memory) with tcgen05.mma, accumulators in TMEM; completion is
+//               signalled to mbarriers with tcgen05.commit.  Warp 1 alone alternates between the
+//               heads where they visit the same blocks; where their lists differ each head gets its
+//               own issuer, so neither waits for the other's softmax
+//   warp 3      idle (it only completes the control warpgroup, which gives most of its registers
 //               to the softmax warpgroups with setmaxnreg)
 //   warps 4-7   softmax warpgroup of head A: a thread owns one query row; tcgen05.ld of S, base-2
 //               online softmax with scale*log2(e) folded in, P rounded to bf16 and written back
@@ -283,6 +285,58 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
 constexpr uint32_t TC_IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(128 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 constexpr uint32_t TC_IDESC_PV = TC_IDESC_QK | (1u << 16);   // B (V) is MN-major
 
+// The eight k-steps of one 128x128x128 product in a single instruction stream: the descriptors of
+// consecutive steps differ only in the 14-bit address field, so each step costs one 32-bit add per
+// operand and the tcgen05.mma itself (the issuing warp shares its scheduler with softmax warps).
+// S (tmem) = Q (smem) K^T (smem): steps 0-3 walk the first 64-element slab in 32-byte strides, 4-7 the second.
+__device__ __forceinline__ void mma_qk_group(uint32_t d_tmem, uint64_t q_desc, uint64_t k_desc) {
+  constexpr uint32_t STEP = 32 >> 4, SLAB = (TC_SLAB_BYTES - 3 * 32) >> 4;
+  asm volatile(
+      "{\n\t.reg .pred pz, po;\n\t.reg .b32 alo, ahi, blo, bhi;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 {alo, ahi}, %1;\n\tmov.b64 {blo, bhi}, %2;\n\t"
+      "setp.ne.b32 pz, 0, 0;\n\tsetp.eq.b32 po, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pz;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %5;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t}"
+      ::"r"(d_tmem), "l"(q_desc), "l"(k_desc), "r"(TC_IDESC_QK), "n"(STEP), "n"(SLAB) : "memory");
+}
+// O (tmem) (+)= P (tmem, 16 bf16 columns = 8 words per step) V (smem, 16 keys = 2048 bytes per step)
+__device__ __forceinline__ void mma_pv_group(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t acc) {
+  constexpr uint32_t VSTEP = 2048 >> 4;
+  asm volatile(
+      "{\n\t.reg .pred pa, po;\n\t.reg .b32 blo, bhi, ta;\n\t.reg .b64 db;\n\t"
+      "mov.b64 {blo, bhi}, %2;\n\tmov.b32 ta, %1;\n\t"
+      "setp.ne.b32 pa, %4, 0;\n\tsetp.eq.b32 po, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], %2, %3, pa;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t}"
+      ::"r"(o_tmem), "r"(p_tmem), "l"(v_desc), "r"(TC_IDESC_PV), "r"(acc), "n"(VSTEP) : "memory");
+}
+
 // Walks the union of two bitmap rows in ascending column order; flags bit h = head h visits it.
 struct PairWalker {
   const uint32_t* wa; const uint32_t* wb;
@@ -353,8 +407,8 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
-    for (int s = 0; s < TC_KSTAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_kempty(s), 1); }
-    for (int s = 0; s < TC_VSTAGES; ++s) { mbar_init(bar_vfull(s), 1); mbar_init(bar_vempty(s), 1); }
+    for (int s = 0; s < TC_KSTAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_kempty(s), 2); }
+    for (int s = 0; s < TC_VSTAGES; ++s) { mbar_init(bar_vfull(s), 1); mbar_init(bar_vempty(s), 2); }
     for (int h = 0; h < 2; ++h) { mbar_init(bar_sfull(h), 1); mbar_init(bar_pready(h), 128); mbar_init(bar_odone(h), 1); }
     *abort_flag = 0;
     fence_barrier_init();
@@ -417,9 +471,32 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int j = (v_issued >= TC_VSTAGES ? v_issued - TC_VSTAGES : 0); j < v_issued; ++j)
         mbar_wait(bar_vfull(j % TC_VSTAGES), (j / TC_VSTAGES) & 1, abort_flag, true);
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp <= 2) {
+    // ------------------------------------------------------------ MMA issuers (warp 1, warp 2)
+    // Two ways to run the CTA's pair of rows, chosen from the two bitmap rows (the same answer in both
+    // warps):
+    //  * alternating: warp 1 issues for both heads in the fixed order P V of A, next Q K^T of A, P V of
+    //    B, next Q K^T of B, which keeps the two softmax warpgroups half a period apart; best where
+    //    the heads visit (nearly) the same blocks.  Warp 2 does nothing.
+    //  * split: warp 1 issues for head A and warp 2 for head B, so a head never waits for the other
+    //    head's softmax on a block it does not visit; best where the lists differ.  Both walk the
+    //    union of the rows in the producer's order and take part in the hand-shake of every tile (a
+    //    tile the head does not visit is passed on as soon as it has landed), so the phase of a ring
+    //    stage can never run ahead of an issuer that skips it.
+    // Every K/V ring stage is released by two arrivals: one per issuer in split mode, both from warp 1
+    // in alternating mode.  These warps share their schedulers with the softmax warps, whose
+    // instruction issue is the bottleneck of the kernel: every instruction here is paid for there.
     if (lane == 0) {
+      const int me = warp - 1;
+      // blocks of head A, of head B and of their union in this row; split where the lists differ enough
+      int cnt_a = 0, cnt_b = 0, cnt_u = 0;
+      for (int i = 0; i <= (r >> 5); ++i) {
+        const int last = r - (i << 5);
+        const uint32_t m = last >= 31 ? 0xffffffffu : ((2u << last) - 1u);
+        const uint32_t wa = __ldg(rowA + i) & m, wb = hasB ? (__ldg(rowB + i) & m) : 0u;
+        cnt_a += __popc(wa); cnt_b += __popc(wb); cnt_u += __popc(wa | wb);
+      }
+      const bool split = hasB && 4 * cnt_u > 5 * max(cnt_a, cnt_b);
       // descriptors differ from a base only in the 14-bit address field: one 64-bit add per operand
       const uint64_t qdA = desc_kmajor(sbase + TC_SMEM_Q), qdB = desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES);
       const uint64_t kd0 = desc_kmajor(sbase + TC_SMEM_K), vd0 = desc_mnmajor(sbase + TC_SMEM_V);
@@ -427,67 +504,99 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint64_t kd = kd0 + uint64_t((ks_stage * TC_TILE_BYTES) >> 4);
         const uint64_t qd = h == 0 ? qdA : qdB;
         const uint32_t ts = tmem + (h == 0 ? 0u : 128u);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t off = uint64_t(((ks >> 2) * TC_SLAB_BYTES + (ks & 3) * 32) >> 4);
-          mma_ss(ts, qd + off, kd + off, TC_IDESC_QK, ks > 0);
-        }
+        mma_qk_group(ts, qd, kd);
         tc_commit(bar_sfull(h));
       };
       auto issue_pv = [&](int h, int vs_stage, bool accumulate) {
         const uint64_t vd = vd0 + uint64_t((vs_stage * TC_TILE_BYTES) >> 4);
         const uint32_t ts = tmem + (h == 0 ? 0u : 128u), to = tmem + (h == 0 ? 256u : 384u);
-        const uint32_t acc0 = accumulate ? 1u : 0u;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ts(to, ts + ks * 8, vd + uint64_t((ks * 2048) >> 4), TC_IDESC_PV, ks > 0 ? 1u : acc0);
+        mma_pv_group(to, ts, vd, accumulate ? 1u : 0u);
       };
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       PairWalker wk; wk.init(rowA, rowB, r);
       int fl, nfl;
       int col = wk.next(fl);
       int i = 0;
-      int nblk[2] = {0, 0};     // P tiles consumed per head
-      if (ok && col >= 0) {
-        ok = mbar_wait(bar_kfull(0), 0, abort_flag);
-        tc_fence_after();
-        if (ok) {
-          for (int h = 0; h < 2; ++h) if (fl & (1 << h)) issue_qk(h, 0);
-          tc_commit(bar_kempty(0));
-        }
-      }
-      while (ok && col >= 0) {
-        const int ncol = wk.next(nfl);
-        const int vs = i % TC_VSTAGES, nks = (i + 1) % TC_KSTAGES;
-        bool v_ready = false, nk_ready = false;
-        const int last_h = (fl & 2) ? 1 : 0;
-        const int nlast_h = (nfl & 2) ? 1 : 0;
-        for (int h = 0; h < 2 && ok; ++h) {
-          if (fl & (1 << h)) {
-            if (!v_ready) { ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
-            if (h == 0) TRACE(2, i, 0); else TRACE(2, i, 4);
-            if (ok) ok = mbar_wait(bar_pready(h), nblk[h] & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            if (h == 0) TRACE(2, i, 1); else TRACE(2, i, 5);
-            issue_pv(h, vs, nblk[h] > 0);
-            if (h == 0) TRACE(2, i, 2); else TRACE(2, i, 6);
-            ++nblk[h];
-            if (h == last_h) tc_commit(bar_vempty(vs));
-          }
-          if (ncol >= 0 && (nfl & (1 << h))) {
-            if (!nk_ready) { ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
-            if (!ok) break;
-            tc_fence_after();
-            issue_qk(h, nks);
-            if (h == nlast_h) tc_commit(bar_kempty(nks));
-            if (h == 0) TRACE(2, i, 3); else TRACE(2, i, 7);
+      if (!split && me == 0) {
+        // ---- alternating mode: warp 1 for both heads
+        int nblk[2] = {0, 0};     // P tiles consumed per head
+        if (ok && col >= 0) {
+          ok = mbar_wait(bar_kfull(0), 0, abort_flag);
+          tc_fence_after();
+          if (ok) {
+            for (int h = 0; h < 2; ++h) if (fl & (1 << h)) issue_qk(h, 0);
+            mbar_arrive(bar_kempty(0));
+            tc_commit(bar_kempty(0));
           }
         }
-        col = ncol; fl = nfl; ++i;
+        while (ok && col >= 0) {
+          const int ncol = wk.next(nfl);
+          const int vs = i % TC_VSTAGES, nks = (i + 1) % TC_KSTAGES;
+          bool v_ready = false, nk_ready = false;
+          const int last_h = (fl & 2) ? 1 : 0;
+          const int nlast_h = (nfl & 2) ? 1 : 0;
+          for (int h = 0; h < 2 && ok; ++h) {
+            if (fl & (1 << h)) {
+              if (!v_ready) { ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
+              if (h == 0) TRACE(2, i, 0); else TRACE(2, i, 4);
+              if (ok) ok = mbar_wait(bar_pready(h), nblk[h] & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              if (h == 0) TRACE(2, i, 1); else TRACE(2, i, 5);
+              issue_pv(h, vs, nblk[h] > 0);
+              if (h == 0) TRACE(2, i, 2); else TRACE(2, i, 6);
+              ++nblk[h];
+              if (h == last_h) { mbar_arrive(bar_vempty(vs)); tc_commit(bar_vempty(vs)); }
+            }
+            if (ncol >= 0 && (nfl & (1 << h))) {
+              if (!nk_ready) { ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
+              if (!ok) break;
+              tc_fence_after();
+              issue_qk(h, nks);
+              if (h == nlast_h) { mbar_arrive(bar_kempty(nks)); tc_commit(bar_kempty(nks)); }
+              if (h == 0) TRACE(2, i, 3); else TRACE(2, i, 7);
+            }
+          }
+          col = ncol; fl = nfl; ++i;
+        }
+        tc_commit(bar_odone(0));
+        tc_commit(bar_odone(1));
+      } else if (split) {
+        // ---- split mode: this thread issues for head `me` and passes the other head's tiles on
+        const int h = me, mine = 1 << me;
+        int np = 0;               // P tiles consumed
+        if (ok && col >= 0) {
+          ok = mbar_wait(bar_kfull(0), 0, abort_flag);
+          if (ok) {
+            if (fl & mine) { tc_fence_after(); issue_qk(h, 0); tc_commit(bar_kempty(0)); }
+            else mbar_arrive(bar_kempty(0));
+          }
+        }
+        while (ok && col >= 0) {
+          const int ncol = wk.next(nfl);
+          const int vs = i % TC_VSTAGES, nks = (i + 1) % TC_KSTAGES;
+          ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag);
+          if (!ok) break;
+          if (fl & mine) {
+            ok = mbar_wait(bar_pready(h), np & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(h, vs, np > 0);
+            ++np;
+            tc_commit(bar_vempty(vs));
+          } else {
+            mbar_arrive(bar_vempty(vs));
+          }
+          if (ncol >= 0) {
+            ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag);
+            if (!ok) break;
+            if (nfl & mine) { tc_fence_after(); issue_qk(h, nks); tc_commit(bar_kempty(nks)); }
+            else mbar_arrive(bar_kempty(nks));
+          }
+          col = ncol; fl = nfl; ++i;
+        }
+        tc_commit(bar_odone(h));
       }
-      tc_commit(bar_odone(0));
-      tc_commit(bar_odone(1));
     }
   }
   } else {

@@ -77,6 +77,39 @@ def test_tc5_matches_oracle_and_generic(n, h, hkv, density):
     assert d.max().item() <= MAX_ABS
 
 
+@pytest.mark.parametrize("n,h,hkv,density", [
+    (8192, 16, 4, 0.08),     # 512 work items, sparse rows that differ between the heads of a pair
+    (6000, 12, 4, 0.5),      # odd pairs (3 heads per KV head), ragged N
+    (4096, 8, 8, 1.0),       # single-head items, dense
+])
+def test_tc5_many_items_per_cta_matches_generic(n, h, hkv, density):
+    """More work items than SMs: every persistent CTA runs several items back to back, so the
+    rings, the Q buffer and the TMEM accumulators are handed from one item to the next."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(n + 3 * h)
+    q = torch.randn(n, h, 128, generator=g).bfloat16().to(dev)
+    k = torch.randn(n, hkv, 128, generator=g).bfloat16().to(dev)
+    v = torch.randn(n, hkv, 128, generator=g).bfloat16().to(dev)
+    nb = -(-n // 128)
+    m = torch.tril(torch.rand(h, nb, nb, generator=g) < density)
+    m[:, :, 0] = True
+    m |= torch.eye(nb, dtype=torch.bool)
+    m[1, 5:9] = False        # rows without any block (also no diagonal) in one head of a pair
+    m[2, 7] = False
+    sets = [torch.nonzero(m[i].reshape(-1)).flatten() for i in range(h)]
+    bm = native.sets_to_bitmap(sets, nb, dev)
+    for _ in range(2):       # twice: the second launch draws from a fresh work counter
+        out_tc5 = _run(q, k, v, bm, "tc5")
+        assert native.load().spf_device_timeouts() == 0, "a bounded wait in the tcgen05 kernel ran out"
+    out_gen = _run(q, k, v, bm, "generic")
+    d = (out_tc5.float() - out_gen.float()).abs()
+    bound = torch.maximum(torch.full_like(d, MAX_ABS), out_gen.float().abs() * 2.0 ** -7)
+    assert bool((d <= bound).all()), f"max abs {d.max().item()}"
+    assert d.mean().item() <= MEAN_ABS
+    # rows that visit nothing come back as zeros
+    assert float(out_tc5[5 * 128:9 * 128, 1].float().abs().max()) == 0.0
+
+
 def test_tc5_large_logits_trigger_rescale():
     """Scores that grow along the row force the running maximum to move by far more than the
     lazy-rescale margin, so the O accumulator in TMEM is rescaled many times."""
