@@ -20,7 +20,7 @@ INCLUDE = os.path.join(ROOT, "include")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(PKG, "libspf_b200.so")
 
-SOURCES = ["spf_api.cu", "spf_pool.cu", "spf_estimate.cu", "spf_select.cu", "spf_attn_generic.cu", "spf_attn_tc5.cu", "spf_decode.cu"]
+SOURCES = ["spf_api.cu", "spf_pool.cu", "spf_estimate.cu", "spf_select.cu", "spf_attn_generic.cu", "spf_attn_tc5.cu", "spf_decode.cu", "spf_estimate_tc5.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "--expt-relaxed-constexpr", "--expt-extended-lambda", "-Xcompiler", "-fPIC",

@@ -319,7 +319,7 @@ int spf_decode_attention(const void* q, int64_t q_stride_h, const void* k, int64
   return decode_attention(p, head_dim, static_cast<cudaStream_t>(stream));
 }
 
-int spf_device_timeouts(void) { return static_cast<int>(tc5_timeout_count()); }
+int spf_device_timeouts(void) { return static_cast<int>(tc5_timeout_count() + est_tc5_timeout_count()); }
 
 int spf_update_pivots(const int32_t* head_flags, const int32_t* slot_of_head, void* state, int n_slots, int n_heads,
                       int nb, double pattern_threshold, void* stream) {

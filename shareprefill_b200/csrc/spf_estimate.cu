@@ -11,6 +11,9 @@
 // rounded to bf16 (its einsum output dtype) and the softmax runs in fp32.
 // Each slash element receives at most two addends (from two adjacent key tiles) on a zeroed
 // buffer, so the atomic adds are order independent.
+#include <cstdlib>
+#include <cstring>
+
 #include "spf_internal.cuh"
 #include "spf_mma.cuh"
 
@@ -167,19 +170,34 @@ __global__ void __launch_bounds__(EST_NT) lastblock_stats_kernel(const EstParams
   cp_async_wait<0>();
 }
 
-__global__ void lastblock_reduce_kernel(const EstParams p) {
-  const int h = blockIdx.x, row = threadIdx.x;  // 128 threads
+constexpr int RED_SLICES = 8;   // tile slices per head, one warpgroup-sized slice of threads each
+
+__global__ void __launch_bounds__(EST_ROWS * RED_SLICES) lastblock_reduce_kernel(const EstParams p) {
+  // thread (slice, row): running (max, sum) over the tiles slice, slice + 8, ...; slices merged in shared memory
+  __shared__ float sm_m[RED_SLICES][EST_ROWS];
+  __shared__ double sm_z[RED_SLICES][EST_ROWS];
+  const int h = blockIdx.x, row = threadIdx.x % EST_ROWS, slice = threadIdx.x / EST_ROWS;
   const float* pm = p.part_m + int64_t(h) * p.ntiles * EST_ROWS + row;
   const float* pl = p.part_l + int64_t(h) * p.ntiles * EST_ROWS + row;
   float m = -INFINITY;
-  for (int t = 0; t < p.ntiles; ++t) m = fmaxf(m, pm[int64_t(t) * EST_ROWS]);
+  for (int t = slice; t < p.ntiles; t += RED_SLICES) m = fmaxf(m, pm[int64_t(t) * EST_ROWS]);
   double z = 0.0;
-  for (int t = 0; t < p.ntiles; ++t) {
+  for (int t = slice; t < p.ntiles; t += RED_SLICES) {
     const float mt = pm[int64_t(t) * EST_ROWS];
     if (mt != -INFINITY) z += static_cast<double>(pl[int64_t(t) * EST_ROWS]) * static_cast<double>(est_exp(mt - m));
   }
-  p.row_m[h * EST_ROWS + row] = m;
-  p.row_z[h * EST_ROWS + row] = static_cast<float>(z);
+  sm_m[slice][row] = m;
+  sm_z[slice][row] = z;
+  __syncthreads();
+  if (slice == 0) {
+    float mm = -INFINITY;
+    for (int s = 0; s < RED_SLICES; ++s) mm = fmaxf(mm, sm_m[s][row]);
+    double zz = 0.0;
+    for (int s = 0; s < RED_SLICES; ++s)
+      if (sm_m[s][row] != -INFINITY) zz += sm_z[s][row] * static_cast<double>(est_exp(sm_m[s][row] - mm));
+    p.row_m[h * EST_ROWS + row] = mm;
+    p.row_z[h * EST_ROWS + row] = static_cast<float>(zz);
+  }
 }
 
 template <int D>
@@ -255,6 +273,10 @@ __global__ void __launch_bounds__(EST_NT, 2) lastblock_profile_kernel(const EstP
   }
 }
 
+void launch_lastblock_reduce(const EstParams& p, cudaStream_t st) {
+  lastblock_reduce_kernel<<<p.n_q_heads, EST_ROWS * RED_SLICES, 0, st>>>(p);
+}
+
 template <int D>
 static int launch_estimate(const EstParams& p, cudaStream_t st) {
   const dim3 grid(ceil_div(p.ntiles, p.tiles_per_cta), p.n_q_heads);
@@ -266,7 +288,7 @@ static int launch_estimate(const EstParams& p, cudaStream_t st) {
   e = cudaFuncSetAttribute(lastblock_profile_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_BYTES + TILE);
   if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
   lastblock_stats_kernel<D><<<grid, EST_NT, 2 * TILE, st>>>(p);
-  lastblock_reduce_kernel<<<p.n_q_heads, EST_ROWS, 0, st>>>(p);
+  lastblock_reduce_kernel<<<p.n_q_heads, EST_ROWS * RED_SLICES, 0, st>>>(p);
   lastblock_profile_kernel<D><<<grid, EST_NT, P_BYTES + TILE, st>>>(p);
   return check_launch();
 }
@@ -274,7 +296,16 @@ static int launch_estimate(const EstParams& p, cudaStream_t st) {
 int lastblock_profile(const EstParams& p, int head_dim, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(p.slash, 0, sizeof(float) * int64_t(p.n_q_heads) * p.n_tokens, st);
   if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
-  if (head_dim == 128) return launch_estimate<128>(p, st);
+  if (head_dim == 128) {
+    // tcgen05 kernels unless SPF_PROFILE_KERNEL=generic asks for the mma.sync ones (used by the tests
+    // to compare the two) or the key tensor cannot be described to TMA
+    const char* force = std::getenv("SPF_PROFILE_KERNEL");
+    if (!(force && std::strcmp(force, "generic") == 0)) {
+      const int rc = lastblock_profile_tc5(p, st);
+      if (rc != SPF_ERR_SHAPE) return rc;
+    }
+    return launch_estimate<128>(p, st);
+  }
   if (head_dim == 64) return launch_estimate<64>(p, st);
   return SPF_ERR_SHAPE;
 }

@@ -118,6 +118,8 @@ struct DecodeParams {
 };
 
 int decode_attention(const DecodeParams& p, int head_dim, cudaStream_t st);
+int lastblock_profile_tc5(const EstParams& p, cudaStream_t st);
+unsigned int est_tc5_timeout_count();
 int sparse_attention_generic(const AttnParams& p, int block_size, int head_dim, cudaStream_t st);
 int sparse_attention_tc5(const AttnParams& p, int n_kv_heads, cudaStream_t st);
 unsigned int tc5_timeout_count();

@@ -1,0 +1,325 @@
+// tcgen05 / TMEM / TMA building blocks shared by the sm_100a kernels (block-sparse attention,
+// last-block profile): mbarrier and TMA wrappers with bounded waits, TMEM loads and stores,
+// shared-memory matrix descriptors for 128-byte swizzled [128][64]-element bf16 slabs, grouped
+// tcgen05.mma issue, and the host-side tensor-map encoder.  Every translation unit that includes
+// this header gets its own timeout counter.
+#pragma once
+
+#include <cuda.h>
+
+#include "spf_internal.cuh"
+
+namespace spf {
+
+constexpr int TC_BS = 128;
+constexpr int TC_D = 128;
+constexpr uint32_t TC_TILE_BYTES = TC_BS * TC_D * 2;        // 32 KiB: one 128x128 bf16 tile
+constexpr uint32_t TC_SLAB_BYTES = TC_TILE_BYTES / 2;       // [128 rows][64 elements]
+
+// bounded device-side waits that gave up (read back by the host after a run)
+static __device__ unsigned int g_tc5_timeouts = 0;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 2000;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false once the CTA has aborted (unless `drain`) or after ~1 s without completion.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          bool drain = false) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  int spins = 0;
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if ((++spins & 63) == 0) {
+      if (*abort_flag && !drain) return false;
+      if (global_ns() - t0 > 1000000000ull) {
+        *abort_flag = 1;
+        atomicAdd(&g_tc5_timeouts, 1u);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+// D(tmem) (+)= A(smem desc) * B(smem desc)
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// D(tmem) (+)= A(tmem) * B(smem desc)
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 32 consecutive columns of this thread's TMEM lane, no wait (pair with tc_wait_ld)
+__device__ __forceinline__ void tmem_ld32_raw(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+// columns whose index exceeds `last` are masked out (-inf)
+__device__ __forceinline__ void mask_after(uint32_t (&r)[32], int last) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (j > last) r[j] = 0xff800000u;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float row_max(const uint32_t (&r)[32]) {
+  float a = __uint_as_float(r[0]), b = __uint_as_float(r[1]);
+#pragma unroll
+  for (int j = 2; j < 30; j += 4) {
+    a = max3(a, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+    b = max3(b, __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+  }
+  return max3(fmaxf(a, b), __uint_as_float(r[30]), __uint_as_float(r[31]));
+}
+__device__ __forceinline__ float fast_exp2(float x);
+// two fp32 lanes in one 64-bit register (packed fp32x2 arithmetic of sm_100)
+__device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
+  unsigned long long d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+  return d;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float& lo, float& hi) {
+  uint32_t a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+  lo = __uint_as_float(a); hi = __uint_as_float(b);
+}
+__device__ __forceinline__ unsigned long long f2_fma(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_from(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));   // first source -> upper half
+  return d;
+}
+// p = 2^(s*scale - m) for 32 scores: packed to bf16 pairs, unrounded values summed into `sum`
+__device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], float scale, float m, uint32_t (&pk)[16], float& sum) {
+  const unsigned long long sc2 = f2_pack(scale, scale), nm2 = f2_pack(-m, -m);
+  unsigned long long acc[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    const unsigned long long x = f2_pack(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+    float y0, y1;
+    f2_unpack(f2_fma(x, sc2, nm2), y0, y1);
+    const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+    acc[(j >> 1) & 3] = f2_add(acc[(j >> 1) & 3], f2_pack(p0, p1));
+    pk[j >> 1] = bf16x2_from(p0, p1);
+  }
+  float a0, a1;
+  f2_unpack(f2_add(f2_add(acc[0], acc[1]), f2_add(acc[2], acc[3])), a0, a1);
+  sum += a0 + a1;
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  tc_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+// 16 packed bf16x2 words -> 16 consecutive columns
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return (static_cast<uint32_t>(__bfloat16_as_ushort(v.y)) << 16) | __bfloat16_as_ushort(v.x);
+}
+
+// shared-memory matrix descriptors, 128-byte swizzle, descriptor version 1
+// K-major operand ([rows][64 elements] slabs, 8-row groups 1024 bytes apart)
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t saddr) {
+  return (uint64_t((saddr >> 4) & 0x3fff)) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// MN-major operand (V: [keys][64 d] slabs; 8-key groups 1024 bytes apart, 64-d slabs 16 KiB apart)
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t saddr) {
+  return (uint64_t((saddr >> 4) & 0x3fff)) | (uint64_t(TC_SLAB_BYTES >> 4) << 16) | (uint64_t(1024 >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// instruction descriptor: bf16 x bf16 -> fp32, M = 128, N = 128
+constexpr uint32_t TC_IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(128 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+constexpr uint32_t TC_IDESC_PV = TC_IDESC_QK | (1u << 16);   // B (V) is MN-major
+
+// The eight k-steps of one 128x128x128 product in a single instruction stream: the descriptors of
+// consecutive steps differ only in the 14-bit address field, so each step costs one 32-bit add per
+// operand and the tcgen05.mma itself (the issuing warp shares its scheduler with softmax warps).
+// S (tmem) = Q (smem) K^T (smem): steps 0-3 walk the first 64-element slab in 32-byte strides, 4-7 the second.
+__device__ __forceinline__ void mma_qk_group(uint32_t d_tmem, uint64_t q_desc, uint64_t k_desc) {
+  constexpr uint32_t STEP = 32 >> 4, SLAB = (TC_SLAB_BYTES - 3 * 32) >> 4;
+  asm volatile(
+      "{\n\t.reg .pred pz, po;\n\t.reg .b32 alo, ahi, blo, bhi;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 {alo, ahi}, %1;\n\tmov.b64 {blo, bhi}, %2;\n\t"
+      "setp.ne.b32 pz, 0, 0;\n\tsetp.eq.b32 po, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pz;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %5;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t"
+      "add.u32 alo, alo, %4;\n\tadd.u32 blo, blo, %4;\n\tmov.b64 da, {alo, ahi};\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t}"
+      ::"r"(d_tmem), "l"(q_desc), "l"(k_desc), "r"(TC_IDESC_QK), "n"(STEP), "n"(SLAB) : "memory");
+}
+// O (tmem) (+)= P (tmem, 16 bf16 columns = 8 words per step) V (smem, 16 keys = 2048 bytes per step)
+__device__ __forceinline__ void mma_pv_group(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t acc) {
+  constexpr uint32_t VSTEP = 2048 >> 4;
+  asm volatile(
+      "{\n\t.reg .pred pa, po;\n\t.reg .b32 blo, bhi, ta;\n\t.reg .b64 db;\n\t"
+      "mov.b64 {blo, bhi}, %2;\n\tmov.b32 ta, %1;\n\t"
+      "setp.ne.b32 pa, %4, 0;\n\tsetp.eq.b32 po, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], %2, %3, pa;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
+      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t}"
+      ::"r"(o_tmem), "r"(p_tmem), "l"(v_desc), "r"(TC_IDESC_PV), "r"(acc), "n"(VSTEP) : "memory");
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// [N][heads][128] bf16 view (strides in elements) as a 3-D tensor (d, token, head); box 64 x 128 x 1
+static bool make_map(CUtensorMap* m, const void* base, int n_tokens, int heads, int64_t sn, int64_t sh) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {cuuint64_t(TC_D), cuuint64_t(n_tokens), cuuint64_t(heads)};
+  const cuuint64_t strides[2] = {cuuint64_t(sn) * 2, cuuint64_t(sh) * 2};
+  const cuuint32_t box[3] = {64, TC_BS, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace spf
