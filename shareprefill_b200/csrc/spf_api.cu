@@ -89,7 +89,7 @@ int spf_lastblock_profile(const void* q, int64_t q_stride_n, int64_t q_stride_h,
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_sn = q_stride_n; p.q_sh = q_stride_h;
   p.k = static_cast<const __nv_bfloat16*>(k); p.k_sn = k_stride_n; p.k_sh = k_stride_h;
   p.n_tokens = n_tokens; p.n_q_heads = n_q_heads; p.group = n_q_heads / n_kv_heads;
-  p.rq = block_size; p.ntiles = ceil_div(n_tokens, 128);
+  p.rq = block_size; p.ntiles = ceil_div(n_tokens, 128); p.n_parts = p.ntiles;
   int tpc = (p.ntiles * n_q_heads) / (148 * 8);
   p.tiles_per_cta = tpc < 1 ? 1 : (tpc > 8 ? 8 : tpc);
   p.sqrt_d = static_cast<float>(std::sqrt(static_cast<double>(head_dim)));

@@ -177,12 +177,12 @@ __global__ void __launch_bounds__(EST_ROWS * RED_SLICES) lastblock_reduce_kernel
   __shared__ float sm_m[RED_SLICES][EST_ROWS];
   __shared__ double sm_z[RED_SLICES][EST_ROWS];
   const int h = blockIdx.x, row = threadIdx.x % EST_ROWS, slice = threadIdx.x / EST_ROWS;
-  const float* pm = p.part_m + int64_t(h) * p.ntiles * EST_ROWS + row;
-  const float* pl = p.part_l + int64_t(h) * p.ntiles * EST_ROWS + row;
+  const float* pm = p.part_m + int64_t(h) * p.n_parts * EST_ROWS + row;
+  const float* pl = p.part_l + int64_t(h) * p.n_parts * EST_ROWS + row;
   float m = -INFINITY;
-  for (int t = slice; t < p.ntiles; t += RED_SLICES) m = fmaxf(m, pm[int64_t(t) * EST_ROWS]);
+  for (int t = slice; t < p.n_parts; t += RED_SLICES) m = fmaxf(m, pm[int64_t(t) * EST_ROWS]);
   double z = 0.0;
-  for (int t = slice; t < p.ntiles; t += RED_SLICES) {
+  for (int t = slice; t < p.n_parts; t += RED_SLICES) {
     const float mt = pm[int64_t(t) * EST_ROWS];
     if (mt != -INFINITY) z += static_cast<double>(pl[int64_t(t) * EST_ROWS]) * static_cast<double>(est_exp(mt - m));
   }
@@ -379,7 +379,7 @@ extern "C" int spf_lastblock_profile_static(const void* q, int64_t q_stride_n, i
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_sn = q_stride_n; p.q_sh = q_stride_h;
   p.k = static_cast<const __nv_bfloat16*>(k); p.k_sn = k_stride_n; p.k_sh = k_stride_h;
   p.n_tokens = n_tokens; p.n_q_heads = n_q_heads; p.group = n_q_heads / n_kv_heads;
-  p.rq = block_size; p.ntiles = ntiles;
+  p.rq = block_size; p.ntiles = ntiles; p.n_parts = ntiles;
   const int tpc = (ntiles * n_q_heads) / (148 * 8);
   p.tiles_per_cta = tpc < 1 ? 1 : (tpc > 8 ? 8 : tpc);
   p.sqrt_d = sqrtf(static_cast<float>(head_dim));

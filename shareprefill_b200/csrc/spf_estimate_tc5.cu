@@ -23,6 +23,8 @@
 // Rounding points are those of the mma.sync version: logits rounded to bf16, softmax in fp32.
 // Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, all roles drain and
 // the kernel returns after recording the event.
+#include <type_traits>
+
 #include "spf_tc5.cuh"
 
 namespace spf {
@@ -182,6 +184,8 @@ lastblock_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const EstTc5Para
       asm volatile("bar.sync 3, 256;" ::: "memory");
     }
     float* dpart_wg = dpart_all + wg * 2048;         // [2 buffers][4 chunks][4 warps][64]
+    // pass 1: running row statistics of the two heads this warpgroup serves
+    float run_m0 = -INFINITY, run_m1 = -INFINITY, run_l0 = 0.f, run_l1 = 0.f;
     int nsync = 0;                                   // uses of the warpgroup barrier so far (its phase)
     // bounded like every other wait: a thread that gave up never strands the others at a hardware barrier
     auto wg_sync = [&]() -> bool {
@@ -221,21 +225,32 @@ lastblock_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const EstTc5Para
             mask_after(s0, last); mask_after(s1, last - 32); mask_after(s2, last - 64); mask_after(s3, last - 96);
           }
           const float mx = fmaxf(fmaxf(row_max(s0), row_max(s1)), fmaxf(row_max(s2), row_max(s3)));
-          const float mref = (mx == -INFINITY ? 0.f : mx) * ET_LOG2E;
-          float sum = 0.f;
+          // running maximum and sum of this row over the CTA's tiles (rescaled when the maximum moves);
+          // one partial per head, row and CTA leaves the kernel
+          float& run_m = (h < 2) ? run_m0 : run_m1;
+          float& run_l = (h < 2) ? run_l0 : run_l1;
+          if (mx > run_m) {
+            run_l *= fast_exp2((run_m - mx) * ET_LOG2E);   // 0 when run_m is -inf
+            run_m = mx;
+          }
+          const float mref = (run_m == -INFINITY ? 0.f : run_m) * ET_LOG2E;
+          float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
           auto add32 = [&](const uint32_t (&r)[32]) {
-            float a = 0.f, b = 0.f;
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              a += fast_exp2(fmaf(__uint_as_float(r[j]), ET_LOG2E, -mref));
-              b += fast_exp2(fmaf(__uint_as_float(r[j + 1]), ET_LOG2E, -mref));
+            for (int j = 0; j < 32; j += 4) {
+              a0 += fast_exp2(fmaf(__uint_as_float(r[j]), ET_LOG2E, -mref));
+              a1 += fast_exp2(fmaf(__uint_as_float(r[j + 1]), ET_LOG2E, -mref));
+              a2 += fast_exp2(fmaf(__uint_as_float(r[j + 2]), ET_LOG2E, -mref));
+              a3 += fast_exp2(fmaf(__uint_as_float(r[j + 3]), ET_LOG2E, -mref));
             }
-            sum += a + b;
           };
           add32(s0); add32(s1); add32(s2); add32(s3);
-          const int64_t base = (int64_t(head) * p.ntiles + tile) * 128 + ln;
-          p.part_m[base] = mx;
-          p.part_l[base] = sum;
+          run_l += (a0 + a1) + (a2 + a3);
+          if (i == ntl - 1) {
+            const int64_t base = (int64_t(head) * p.n_parts + blockIdx.x) * 128 + ln;
+            p.part_m[base] = run_m;
+            p.part_l[base] = run_l;
+          }
         } else {
           // thread = key c0 + ln; columns = query rows 0..127.  Row i sees this key if kpos <= q0 + i.
           const int kpos = c0 + ln;
@@ -247,33 +262,52 @@ lastblock_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const EstTc5Para
           // that lane m receives the value of lane (m + j) mod 32, whose l - j is m (no wrap) or m - 32
           // (wrap): two running sums per lane, `lo` for slot 32(q-c) + 127 + m and `hi` for 32 less.
           // One shuffle per element, no shared-memory traffic until the chunk is done.
-          float vs0 = 0.f, vs1 = 0.f;
+          float vs0 = 0.f, vs1 = 0.f, vs2 = 0.f, vs3 = 0.f;
           float* dpart = dpart_wg + (nsync & 1) * 1024;   // buffers alternate from tile to tile
           float* part = dpart + quarter * 64;        // [chunk][warp][lo 0..31 | hi 0..31]
-          auto chunk = [&](const uint32_t (&r)[32], int c) {
-            float lo = 0.f, hi = 0.f;
+          // lane m takes the unwrapped values for j < 32 - m and the wrapped ones after: one running
+          // sum, `lo` is its value after step 31 - m and `hi` the rest
+          auto chunk = [&](const uint32_t (&r)[32], int c, auto masked) {
+            float run = 0.f, lo = 0.f;
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const float4 t4 = *reinterpret_cast<const float4*>(tb + 32 * c + j);
-              const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
-              const uint32_t pk0 = bf16x2_from(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-              const uint32_t pk1 = bf16x2_from(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              const uint32_t xb[4] = {pk0 << 16, pk0 & 0xffff0000u, pk1 << 16, pk1 & 0xffff0000u};
+            for (int j = 0; j < 32; j += 8) {
+              // eight values at a time: exponentials, then the eight rotations, then the running sum, so
+              // that no instruction waits for the result of the one just before it
+              const float4 ta = *reinterpret_cast<const float4*>(tb + 32 * c + j);
+              const float4 tc = *reinterpret_cast<const float4*>(tb + 32 * c + j + 4);
+              const float tv[8] = {ta.x, ta.y, ta.z, ta.w, tc.x, tc.y, tc.z, tc.w};
+              uint32_t xb[8];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int jj = j + e, irow = 32 * c + jj;
-                float pv = fast_exp2(fmaf(__uint_as_float(xb[e]), ET_LOG2E, -tv[e]));
-                if (irow < first) pv = 0.f;
-                if (e & 1) vs1 += pv; else vs0 += pv;
-                const float rot = __shfl_sync(0xffffffffu, pv, (lane + jj) & 31);
-                if (lane + jj < 32) lo += rot; else hi += rot;
+              for (int e = 0; e < 8; e += 2) {
+                const uint32_t pk = bf16x2_from(__uint_as_float(r[j + e]), __uint_as_float(r[j + e + 1]));
+                xb[e] = pk << 16; xb[e + 1] = pk & 0xffff0000u;
+              }
+              float pv[8], rot[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                pv[e] = fast_exp2(fmaf(__uint_as_float(xb[e]), ET_LOG2E, -tv[e]));
+                if (decltype(masked)::value && 32 * c + j + e < first) pv[e] = 0.f;
+              }
+#pragma unroll
+              for (int e = 0; e < 8; ++e) rot[e] = __shfl_sync(0xffffffffu, pv[e], lane + j + e);   // source lane modulo 32
+              vs0 += pv[0] + pv[4]; vs1 += pv[1] + pv[5]; vs2 += pv[2] + pv[6]; vs3 += pv[3] + pv[7];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                run += rot[e];
+                if (lane == 31 - (j + e)) lo = run;
               }
             }
             part[c * 256 + lane] = lo;
-            part[c * 256 + 32 + lane] = hi;
+            part[c * 256 + 32 + lane] = run - lo;
           };
-          chunk(s0, 0); chunk(s1, 1); chunk(s2, 2); chunk(s3, 3);
-          if (kpos < p.n_tokens) p.vertical[int64_t(head) * p.n_tokens + kpos] = (vs0 + vs1) * inv_rows;
+          if (c0 + TC_BS - 1 > q0) {   // only the last tiles see the causal mask (and keys past the end)
+            chunk(s0, 0, std::true_type{}); chunk(s1, 1, std::true_type{});
+            chunk(s2, 2, std::true_type{}); chunk(s3, 3, std::true_type{});
+          } else {
+            chunk(s0, 0, std::false_type{}); chunk(s1, 1, std::false_type{});
+            chunk(s2, 2, std::false_type{}); chunk(s3, 3, std::false_type{});
+          }
+          if (kpos < p.n_tokens) p.vertical[int64_t(head) * p.n_tokens + kpos] = ((vs0 + vs1) + (vs2 + vs3)) * inv_rows;
           ok = wg_sync();
           if (!ok) break;
           // slot x collects, over chunks c and warps w, lo[m] with m = x - 127 - 32(w-c) and hi[m] with
@@ -331,13 +365,14 @@ int lastblock_profile_tc5(const EstParams& e, cudaStream_t st) {
   const int tpc = ceil_div(e.ntiles, chunks);
   pp.tiles_per_cta = tpc;
   const dim3 grid(ceil_div(e.ntiles, tpc), rows);
+  pp.e.n_parts = int(grid.x);   // pass 1 leaves one partial per head, row and CTA
   cudaError_t err = cudaFuncSetAttribute(lastblock_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          int(ET_SMEM_TOTAL));
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(lastblock_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ET_SMEM_TOTAL));
   if (err != cudaSuccess) { note_cuda_error(err); return SPF_ERR_LAUNCH; }
   lastblock_tc5_kernel<false><<<grid, ET_THREADS, ET_SMEM_TOTAL, st>>>(mk, pp);
-  launch_lastblock_reduce(e, st);
+  launch_lastblock_reduce(pp.e, st);
   lastblock_tc5_kernel<true><<<grid, ET_THREADS, ET_SMEM_TOTAL, st>>>(mk, pp);
   return check_launch();
 }

@@ -24,9 +24,10 @@ struct EstParams {
   const __nv_bfloat16* q; int64_t q_sn, q_sh;
   const __nv_bfloat16* k; int64_t k_sn, k_sh;
   int n_tokens, n_q_heads, group, rq, ntiles, tiles_per_cta;
+  int n_parts;            // partial (max, sum) pairs per head and row that pass 1 leaves (mma.sync path: ntiles)
   float sqrt_d;           // queries are divided by it
-  float* part_m;          // [H][ntiles][128]
-  float* part_l;          // [H][ntiles][128]
+  float* part_m;          // [H][n_parts][128] (allocated for ntiles)
+  float* part_l;          // [H][n_parts][128]
   float* row_m;           // [H][128]
   float* row_z;           // [H][128]
   float* vertical;        // [H][N]
