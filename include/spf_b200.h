@@ -124,7 +124,8 @@ int spf_profile_budgets(const float* vertical, const float* slash, int n_heads, 
 
 /* ---------------------------------------------------------------- pooled last-row estimate
  * avg_qk[h][b] = softmax_b( mean(last queries / sqrt(D)) . avg_k[b] )
- * (attn/attention_sharing.py:197-200).  avg_qk: fp32 [H][nb].
+ * (attn/attention_sharing.py:197-200).  avg_qk: fp32 [H][nb].  avg_k: the pooled keys of
+ * spf_pool_qk, bf16 [nb][Hkv][D] contiguous, 16-byte aligned.
  */
 int spf_pooled_last_row(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                         const void* avg_k, int n_tokens, int n_q_heads, int n_kv_heads,

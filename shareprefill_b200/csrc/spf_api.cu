@@ -125,6 +125,7 @@ int spf_pooled_last_row(const void* q, int64_t q_stride_n, int64_t q_stride_h, c
   if (!q || !avg_k || !avg_qk) return SPF_ERR_NULL;
   int rc = check_shape(n_tokens, n_q_heads, n_kv_heads, head_dim, block_size);
   if (rc) return rc;
+  if (!aligned16(avg_k)) return SPF_ERR_ALIGN;   // pooled key rows are read 16 bytes at a time
   LastRowParams p;
   p.q = static_cast<const __nv_bfloat16*>(q); p.q_sn = q_stride_n; p.q_sh = q_stride_h;
   p.avg_k = static_cast<const __nv_bfloat16*>(avg_k);

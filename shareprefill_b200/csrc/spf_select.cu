@@ -72,13 +72,22 @@ __global__ void __launch_bounds__(256) pooled_last_row_kernel(const LastRowParam
     }
   }
   __syncthreads();
+  // one thread per key block: its pooled key row (head_dim bf16, 16-byte loads) against the mean query
+  // in shared memory; the blocks of a thread are independent, so their loads overlap
   float lmax = -INFINITY;
-  for (int b = warp; b < p.nb; b += 8) {
-    const __nv_bfloat16* kr = p.avg_k + (int64_t(b) * p.n_kv_heads + kvh) * p.head_dim;
-    float acc = 0.f;
-    for (int d = lane; d < p.head_dim; d += 32) acc += qm[d] * __bfloat162float(kr[d]);
-    acc = bf16_round(warp_sum(acc));
-    if (lane == 0) dyn[b] = acc;
+  for (int b = tid; b < p.nb; b += 256) {
+    const uint4* kr = reinterpret_cast<const uint4*>(p.avg_k + (int64_t(b) * p.n_kv_heads + kvh) * p.head_dim);
+    float a0 = 0.f, a1 = 0.f;
+    for (int c = 0; c < p.head_dim / 8; ++c) {
+      const uint4 v = __ldg(kr + c);
+      const float* q8 = qm + c * 8;
+      a0 += q8[0] * __uint_as_float(v.x << 16) + q8[2] * __uint_as_float(v.y << 16) +
+            q8[4] * __uint_as_float(v.z << 16) + q8[6] * __uint_as_float(v.w << 16);
+      a1 += q8[1] * __uint_as_float(v.x & 0xffff0000u) + q8[3] * __uint_as_float(v.y & 0xffff0000u) +
+            q8[5] * __uint_as_float(v.z & 0xffff0000u) + q8[7] * __uint_as_float(v.w & 0xffff0000u);
+    }
+    const float acc = bf16_round(a0 + a1);
+    dyn[b] = acc;
     lmax = fmaxf(lmax, acc);
   }
   const float m = block_max(lmax, red_f);
