@@ -69,13 +69,27 @@ __device__ CoverResult cover_select(Load load, int n, float thr, int rule, int s
     __syncthreads();
     for (int b = threadIdx.x; b < nbins; b += blockDim.x) { sh->cnt[b] = 0; sh->sum[b] = 0ull; }
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const float x = load(i);
-      const unsigned int key = __float_as_uint(x) & 0x7fffffffu;
-      if (key == 0u || (key >> hi_shift) != prefix) continue;
-      const unsigned int b = (key >> shift) & (nbins - 1);
-      atomicAdd(&sh->cnt[b], 1u);
-      atomicAdd(&sh->sum[b], __double2ull_rz(static_cast<double>(x) * scale));
+    // four elements per thread and trip, loaded before any is used (one load in flight per thread
+    // leaves the loop waiting on memory); elements past the end read as zero, which is skipped.
+    // (Adding up the lanes that share a bin before touching the histogram - match_any plus warp
+    // reductions - was measured slower than the plain shared-memory atomics: 312 against 191 us for
+    // 64 vectors of 128K elements.)
+    for (int i0 = threadIdx.x; i0 < n; i0 += 4 * blockDim.x) {
+      float xs[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        xs[u] = i < n ? load(i) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float x = xs[u];
+        const unsigned int key = __float_as_uint(x) & 0x7fffffffu;
+        if (key == 0u || (key >> hi_shift) != prefix) continue;
+        const unsigned int b = (key >> shift) & (nbins - 1);
+        atomicAdd(&sh->cnt[b], 1u);
+        atomicAdd(&sh->sum[b], __double2ull_rz(static_cast<double>(x) * scale));
+      }
     }
     __syncthreads();
     if (threadIdx.x < 32) {
