@@ -210,6 +210,7 @@ int spf_query_aware_scores(const void* avg_q, const void* avg_k, const int32_t* 
   if (!avg_q || !avg_k || !scores) return SPF_ERR_NULL;
   if (!supported_head_dim(head_dim) || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads) return SPF_ERR_SHAPE;
   if (n_q_heads > SPF_MAX_HEADS || nb <= 0 || nb > SPF_MAX_BLOCKS) return SPF_ERR_TOO_LARGE;
+  if (!aligned16(avg_k)) return SPF_ERR_ALIGN;   // pooled key rows are read 16 bytes at a time
   QaScoreParams p;
   p.avg_q = static_cast<const __nv_bfloat16*>(avg_q); p.avg_k = static_cast<const __nv_bfloat16*>(avg_k);
   p.head_flags = head_flags; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.head_dim = head_dim;

@@ -49,7 +49,11 @@ __device__ __forceinline__ bool cover_ok(unsigned long long fx, double inv_scale
 
 // All threads of the block call this with the same arguments.  `load(i)` returns element i
 // (non-negative fp32) for i in [0, n).  Exact zeros are skipped (they never move a prefix).
-template <class Load>
+// RUN_LENGTH is for inputs in which the successive elements of a thread (one block stride apart)
+// mostly share a bin - a row-major score matrix whose rows are softmaxes over a long causal prefix,
+// where a block stride is about one row: a thread then keeps (bin, count, sum) of its current run
+// in registers and touches the histogram only when the bin changes.
+template <bool RUN_LENGTH = false, class Load>
 __device__ CoverResult cover_select(Load load, int n, float thr, int rule, int scale_bits,
                                     CoverShared* sh) {
   const double scale = exp2(static_cast<double>(scale_bits));
@@ -71,9 +75,11 @@ __device__ CoverResult cover_select(Load load, int n, float thr, int rule, int s
     __syncthreads();
     // four elements per thread and trip, loaded before any is used (one load in flight per thread
     // leaves the loop waiting on memory); elements past the end read as zero, which is skipped.
-    // (Adding up the lanes that share a bin before touching the histogram - match_any plus warp
-    // reductions - was measured slower than the plain shared-memory atomics: 312 against 191 us for
-    // 64 vectors of 128K elements.)
+    // (Adding up the lanes that share a bin with match_any before touching the histogram was measured
+    // slower than the plain shared-memory atomics on the token profiles: 312 against 191 us for 64
+    // vectors of 128K elements.)
+    unsigned int run_bin = 0xffffffffu, run_cnt = 0;   // RUN_LENGTH: the thread's current run
+    unsigned long long run_fx = 0ull;
     for (int i0 = threadIdx.x; i0 < n; i0 += 4 * blockDim.x) {
       float xs[4];
 #pragma unroll
@@ -87,10 +93,20 @@ __device__ CoverResult cover_select(Load load, int n, float thr, int rule, int s
         const unsigned int key = __float_as_uint(x) & 0x7fffffffu;
         if (key == 0u || (key >> hi_shift) != prefix) continue;
         const unsigned int b = (key >> shift) & (nbins - 1);
-        atomicAdd(&sh->cnt[b], 1u);
-        atomicAdd(&sh->sum[b], __double2ull_rz(static_cast<double>(x) * scale));
+        const unsigned long long fx = __double2ull_rz(static_cast<double>(x) * scale);
+        if (RUN_LENGTH) {
+          if (b != run_bin) {
+            if (run_cnt) { atomicAdd(&sh->cnt[run_bin], run_cnt); atomicAdd(&sh->sum[run_bin], run_fx); }
+            run_bin = b; run_cnt = 0; run_fx = 0ull;
+          }
+          ++run_cnt; run_fx += fx;
+        } else {
+          atomicAdd(&sh->cnt[b], 1u);
+          atomicAdd(&sh->sum[b], fx);
+        }
       }
     }
+    if (RUN_LENGTH && run_cnt) { atomicAdd(&sh->cnt[run_bin], run_cnt); atomicAdd(&sh->sum[run_bin], run_fx); }
     __syncthreads();
     if (threadIdx.x < 32) {
       const int lane = threadIdx.x;

@@ -263,34 +263,63 @@ __global__ void __launch_bounds__(1024) build_vs_bitmap_kernel(const VsParams p)
 
 // ------------------------------------------------------------------ query-aware scores
 
-// One warp per query block row: logits against the causal prefix of key blocks, rounded to
-// bf16 (the reference's bf16 einsum), fp32 softmax, zeros above the diagonal.
+// A CTA owns eight query block rows of one head.  A thread takes key blocks c, c + 256, ...: the pooled
+// key row is read once (16-byte loads) and used for all eight rows, whose scaled mean queries sit in
+// shared memory.  Logits are rounded to bf16 (the reference's bf16 einsum), the softmax over the
+// causal prefix runs in fp32, one warp per row; zeros above the diagonal.
+// (Four rows per CTA beyond 4096 blocks, where eight rows of logits no longer fit in shared memory.)
+template <int QAS_ROWS>
 __global__ void __launch_bounds__(256) query_aware_scores_kernel(const QaScoreParams p) {
+  extern __shared__ float qa_dyn[];               // logits [QAS_ROWS][nb], then q [QAS_ROWS][D]
   const int h = blockIdx.y;
   if (p.head_flags && !(p.head_flags[h] & SPF_HEAD_QUERY_AWARE)) return;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = blockIdx.x * 8 + warp;
-  if (r >= p.nb) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r0 = blockIdx.x * QAS_ROWS;
+  const int rows = min(QAS_ROWS, p.nb - r0);
   const int kvh = h / (p.n_q_heads / p.n_kv_heads);
-  const int D = p.head_dim, per = D / 32;   // 2 or 4 elements per lane
-  float qv[4];
-  const __nv_bfloat16* qr = p.avg_q + (int64_t(r) * p.n_q_heads + h) * D + lane * per;
-  for (int e = 0; e < per; ++e) qv[e] = bf16_round(__bfloat162float(qr[e]) / p.sqrt_d);
-  float* out = p.scores + (int64_t(h) * p.nb + r) * p.nb;
-  float mx = -INFINITY;
-  for (int c = 0; c <= r; ++c) {
-    const __nv_bfloat16* kr = p.avg_k + (int64_t(c) * p.n_kv_heads + kvh) * D + lane * per;
-    float acc = 0.f;
-    for (int e = 0; e < per; ++e) acc += qv[e] * __bfloat162float(kr[e]);
-    acc = bf16_round(warp_sum(acc));
-    if (lane == 0) out[c] = acc;
-    mx = fmaxf(mx, acc);
+  const int D = p.head_dim;
+  float* logit = qa_dyn;
+  float* qs = qa_dyn + QAS_ROWS * p.nb;
+  for (int i = tid; i < QAS_ROWS * D; i += 256) {
+    const int rr = i / D, d = i % D;
+    qs[i] = rr < rows ? bf16_round(__bfloat162float(p.avg_q[(int64_t(r0 + rr) * p.n_q_heads + h) * D + d]) / p.sqrt_d) : 0.f;
   }
-  __syncwarp();
-  double z = 0.0;
-  for (int c = lane; c <= r; c += 32) z += static_cast<double>(expf(out[c] - mx));
-  const float zf = static_cast<float>(warp_sum(z));
-  for (int c = lane; c < p.nb; c += 32) out[c] = (c <= r) ? expf(out[c] - mx) / zf : 0.f;
+  __syncthreads();
+  const int c_end = r0 + rows;                    // key blocks 0 .. r0 + rows - 1 are needed by some row
+  for (int c = tid; c < c_end; c += 256) {
+    const uint4* kr = reinterpret_cast<const uint4*>(p.avg_k + (int64_t(c) * p.n_kv_heads + kvh) * D);
+    float acc[QAS_ROWS];
+#pragma unroll
+    for (int rr = 0; rr < QAS_ROWS; ++rr) acc[rr] = 0.f;
+    for (int ch = 0; ch < D / 8; ++ch) {
+      const uint4 v = __ldg(kr + ch);
+      const float kf[8] = {__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                           __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u),
+                           __uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
+                           __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u)};
+#pragma unroll
+      for (int rr = 0; rr < QAS_ROWS; ++rr) {
+        const float* q8 = qs + rr * D + ch * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[rr] = fmaf(q8[e], kf[e], acc[rr]);
+      }
+    }
+#pragma unroll
+    for (int rr = 0; rr < QAS_ROWS; ++rr) logit[rr * p.nb + c] = bf16_round(acc[rr]);
+  }
+  __syncthreads();
+  if (warp < rows) {
+    const int r = r0 + warp;
+    const float* lg = logit + warp * p.nb;
+    float mx = -INFINITY;
+    for (int c = lane; c <= r; c += 32) mx = fmaxf(mx, lg[c]);
+    mx = warp_max(mx);
+    double z = 0.0;
+    for (int c = lane; c <= r; c += 32) z += static_cast<double>(expf(lg[c] - mx));
+    const float zf = static_cast<float>(warp_sum(z));
+    float* out = p.scores + (int64_t(h) * p.nb + r) * p.nb;
+    for (int c = lane; c < p.nb; c += 32) out[c] = (c <= r) ? expf(lg[c] - mx) / zf : 0.f;
+  }
 }
 
 // ------------------------------------------------------------------ query-aware select
@@ -302,7 +331,7 @@ __global__ void __launch_bounds__(1024) query_aware_select_kernel(const QaSelect
   const float* x = p.scores + int64_t(h) * p.nb * p.nb;
   const int n = p.nb * p.nb;
   auto load = [x](int i) { return __ldg(x + i); };
-  const CoverResult r = cover_select(load, n, p.thr, COVER_PREFIX_LE, p.scale_bits, &sh);
+  const CoverResult r = cover_select<true>(load, n, p.thr, COVER_PREFIX_LE, p.scale_bits, &sh);
   uint32_t* bm = p.bitmap + int64_t(h) * p.nb * p.nbw;
   const bool ranked = cover_needs_tie_rank(r);
   unsigned int running = 0;
@@ -316,7 +345,13 @@ __global__ void __launch_bounds__(1024) query_aware_select_kernel(const QaSelect
     const int row = in ? i / p.nb : 0, c = in ? i % p.nb : 0;
     // exact zeros are never part of a cover unless everything is; keep to the causal triangle
     const bool keep = in && c <= row && (r.all || (key != 0u && cover_keeps(r, key, rank)));
-    if (keep) atomicOr(&bm[int64_t(row) * p.nbw + (c >> 5)], 1u << (c & 31));
+    if ((p.nb & 31) == 0) {
+      // the 32 elements of a warp are the 32 bits of one bitmap word: one atomic per word
+      const unsigned int word = __ballot_sync(0xffffffffu, keep);
+      if ((threadIdx.x & 31) == 0 && word) atomicOr(&bm[int64_t(row) * p.nbw + (c >> 5)], word);
+    } else if (keep) {
+      atomicOr(&bm[int64_t(row) * p.nbw + (c >> 5)], 1u << (c & 31));
+    }
   }
 }
 
@@ -519,7 +554,14 @@ int launch_vs_bitmap(const VsParams& p, int n_heads, cudaStream_t st) {
   return check_launch();
 }
 int launch_qa_scores(const QaScoreParams& p, cudaStream_t st) {
-  query_aware_scores_kernel<<<dim3(ceil_div(p.nb, 8), p.n_q_heads), 256, 0, st>>>(p);
+  const int rows = p.nb > 4096 ? 4 : 8;
+  const size_t smem = (size_t(rows) * p.nb + size_t(rows) * p.head_dim) * sizeof(float);
+  auto kern = rows == 8 ? query_aware_scores_kernel<8> : query_aware_scores_kernel<4>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
+  }
+  kern<<<dim3(ceil_div(p.nb, rows), p.n_q_heads), 256, smem, st>>>(p);
   return check_launch();
 }
 int launch_qa_select(const QaSelectParams& p, int n_heads, cudaStream_t st) {
