@@ -331,9 +331,36 @@ __global__ void __launch_bounds__(1024) query_aware_select_kernel(const QaSelect
   const float* x = p.scores + int64_t(h) * p.nb * p.nb;
   const int n = p.nb * p.nb;
   auto load = [x](int i) { return __ldg(x + i); };
-  const CoverResult r = cover_select<true>(load, n, p.thr, COVER_PREFIX_LE, p.scale_bits, &sh);
+  const CoverResult r = cover_select<true>(load, n, p.thr, COVER_PREFIX_LE, p.scale_bits, &sh, x);
   uint32_t* bm = p.bitmap + int64_t(h) * p.nb * p.nbw;
   const bool ranked = cover_needs_tie_rank(r);
+  if (!ranked && (p.nb & 31) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+    // no ties to rank: 16 bytes per load; a thread's four elements are four neighbouring bits of a
+    // bitmap word and eight neighbouring lanes make up the word
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    const int n4 = n >> 2, lane = threadIdx.x & 31;
+    const int n4_round = ((n4 + blockDim.x - 1) / blockDim.x) * blockDim.x;
+    for (int i = threadIdx.x; i < n4_round; i += blockDim.x) {
+      const bool in = i < n4;
+      const float4 v = in ? __ldg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const int e0 = in ? i * 4 : 0;
+      const int row = e0 / p.nb, c0 = e0 % p.nb;
+      const float vs[4] = {v.x, v.y, v.z, v.w};
+      unsigned int nib = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const unsigned int key = __float_as_uint(vs[e]) & 0x7fffffffu;
+        const bool keep = in && (c0 + e) <= row && (r.all || (key != 0u && cover_keeps(r, key, 0u)));
+        nib |= (keep ? 1u : 0u) << e;
+      }
+      unsigned int word = nib << (4 * (lane & 7));
+      word |= __shfl_xor_sync(0xffffffffu, word, 1);
+      word |= __shfl_xor_sync(0xffffffffu, word, 2);
+      word |= __shfl_xor_sync(0xffffffffu, word, 4);
+      if ((lane & 7) == 0 && word) atomicOr(&bm[int64_t(row) * p.nbw + (c0 >> 5)], word);
+    }
+    return;
+  }
   unsigned int running = 0;
   const int n_round = ((n + blockDim.x - 1) / blockDim.x) * blockDim.x;
   for (int i = threadIdx.x; i < n_round; i += blockDim.x) {
