@@ -47,6 +47,18 @@ __device__ __forceinline__ bool cover_ok(unsigned long long fx, double inv_scale
   return rule == COVER_PREFIX_LE ? (f <= thr) : (f < thr);
 }
 
+// floor(x * 2^scale_bits) for a positive normal fp32 x (key = its bit pattern), by shifting the
+// mantissa: the same value as __double2ull_rz(double(x) * 2^scale_bits) at a fraction of the
+// instructions (the histogram passes are bound by instruction issue).
+__device__ __forceinline__ unsigned long long cover_fixed(float x, unsigned int key, int scale_bits, double scale) {
+  const int eb = static_cast<int>(key >> 23);
+  const int sh = eb - 150 + scale_bits;
+  const unsigned long long m = static_cast<unsigned long long>((key & 0x7fffffu) | 0x800000u);
+  if (eb != 0 && sh >= 0 && sh <= 40) return m << sh;
+  if (eb != 0 && sh < 0) return sh > -24 ? (m >> (-sh)) : 0ull;
+  return __double2ull_rz(static_cast<double>(x) * scale);   // denormals and values that would overflow
+}
+
 // All threads of the block call this with the same arguments.  `load(i)` returns element i
 // (non-negative fp32) for i in [0, n).  Exact zeros are skipped (they never move a prefix).
 // RUN_LENGTH is for inputs in which the successive elements of a thread (one block stride apart)
@@ -87,7 +99,7 @@ __device__ CoverResult cover_select(Load load, int n, float thr, int rule, int s
       const unsigned int key = __float_as_uint(x) & 0x7fffffffu;
       if (key == 0u || (key >> hi_shift) != prefix) return;
       const unsigned int b = (key >> shift) & (nbins - 1);
-      const unsigned long long fx = __double2ull_rz(static_cast<double>(x) * scale);
+      const unsigned long long fx = cover_fixed(x, key, scale_bits, scale);
       if (RUN_LENGTH) {
         if (b != run_bin) {
           if (run_cnt) { atomicAdd(&sh->cnt[run_bin], run_cnt); atomicAdd(&sh->sum[run_bin], run_fx); }
@@ -213,8 +225,9 @@ __device__ __forceinline__ unsigned int block_flag_rank(bool flag, unsigned int*
                                                        unsigned int* scan /*[32] shared*/) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
   const unsigned int m = __ballot_sync(0xffffffffu, flag);
+  // most chunks hold no flagged element: one barrier settles that and nobody needs a rank
+  if (!__syncthreads_or(m != 0u)) return *running;
   const unsigned int in_warp = __popc(m & ((1u << lane) - 1u));
-  __syncthreads();
   if (lane == 0) scan[w] = __popc(m);
   __syncthreads();
   unsigned int before = 0, total = 0;

@@ -340,11 +340,13 @@ __global__ void __launch_bounds__(1024) query_aware_select_kernel(const QaSelect
     const float4* x4 = reinterpret_cast<const float4*>(x);
     const int n4 = n >> 2, lane = threadIdx.x & 31;
     const int n4_round = ((n4 + blockDim.x - 1) / blockDim.x) * blockDim.x;
-    for (int i = threadIdx.x; i < n4_round; i += blockDim.x) {
+    // (row, column) of the thread's first element, advanced by one block stride per trip: no division
+    int row = (threadIdx.x * 4) / p.nb, c0 = (threadIdx.x * 4) % p.nb;
+    const int step_rows = (blockDim.x * 4) / p.nb, step_cols = (blockDim.x * 4) % p.nb;
+    for (int i = threadIdx.x; i < n4_round; i += blockDim.x, row += step_rows, c0 += step_cols) {
+      if (c0 >= p.nb) { c0 -= p.nb; ++row; }
       const bool in = i < n4;
       const float4 v = in ? __ldg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-      const int e0 = in ? i * 4 : 0;
-      const int row = e0 / p.nb, c0 = e0 % p.nb;
       const float vs[4] = {v.x, v.y, v.z, v.w};
       unsigned int nib = 0;
 #pragma unroll
@@ -363,13 +365,15 @@ __global__ void __launch_bounds__(1024) query_aware_select_kernel(const QaSelect
   }
   unsigned int running = 0;
   const int n_round = ((n + blockDim.x - 1) / blockDim.x) * blockDim.x;
-  for (int i = threadIdx.x; i < n_round; i += blockDim.x) {
+  int row = threadIdx.x / p.nb, c = threadIdx.x % p.nb;
+  const int step_rows = blockDim.x / p.nb, step_cols = blockDim.x % p.nb;
+  for (int i = threadIdx.x; i < n_round; i += blockDim.x, row += step_rows, c += step_cols) {
+    if (c >= p.nb) { c -= p.nb; ++row; }
     const bool in = i < n;
     const float v = in ? __ldg(x + i) : 0.f;
     const unsigned int key = __float_as_uint(v) & 0x7fffffffu;
     unsigned int rank = 0;
     if (ranked) rank = block_flag_rank(in && key == r.key_thr && key != 0u, &running, sh.scan_cnt);
-    const int row = in ? i / p.nb : 0, c = in ? i % p.nb : 0;
     // exact zeros are never part of a cover unless everything is; keep to the causal triangle
     const bool keep = in && c <= row && (r.all || (key != 0u && cover_keeps(r, key, rank)));
     if ((p.nb & 31) == 0) {
