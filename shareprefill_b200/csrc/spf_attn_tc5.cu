@@ -205,16 +205,20 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // Every K/V ring stage is released by two arrivals: one per issuer in split mode, both from warp 1
     // in alternating mode.  These warps share their schedulers with the softmax warps, whose
     // instruction issue is the bottleneck of the kernel: every instruction here is paid for there.
+    // blocks of head A, of head B and of their union in this row (a lane per bitmap word, so the
+    // words arrive in one memory latency); split where the lists differ enough
+    int cnt_a = 0, cnt_b = 0, cnt_u = 0;
+    for (int i = lane; i <= (r >> 5); i += 32) {
+      const int last = r - (i << 5);
+      const uint32_t m = last >= 31 ? 0xffffffffu : ((2u << last) - 1u);
+      const uint32_t wa = __ldg(rowA + i) & m, wb = hasB ? (__ldg(rowB + i) & m) : 0u;
+      cnt_a += __popc(wa); cnt_b += __popc(wb); cnt_u += __popc(wa | wb);
+    }
+    cnt_a = __reduce_add_sync(0xffffffffu, cnt_a);
+    cnt_b = __reduce_add_sync(0xffffffffu, cnt_b);
+    cnt_u = __reduce_add_sync(0xffffffffu, cnt_u);
     if (lane == 0) {
       const int me = warp - 1;
-      // blocks of head A, of head B and of their union in this row; split where the lists differ enough
-      int cnt_a = 0, cnt_b = 0, cnt_u = 0;
-      for (int i = 0; i <= (r >> 5); ++i) {
-        const int last = r - (i << 5);
-        const uint32_t m = last >= 31 ? 0xffffffffu : ((2u << last) - 1u);
-        const uint32_t wa = __ldg(rowA + i) & m, wb = hasB ? (__ldg(rowB + i) & m) : 0u;
-        cnt_a += __popc(wa); cnt_b += __popc(wb); cnt_u += __popc(wa | wb);
-      }
       const bool split = hasB && 4 * cnt_u > 5 * max(cnt_a, cnt_b);
       // descriptors differ from a base only in the 14-bit address field: one 64-bit add per operand
       const uint64_t qdA = desc_kmajor(sbase + TC_SMEM_Q), qdB = desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES);
