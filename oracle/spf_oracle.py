@@ -272,19 +272,35 @@ class SharingOracle:
         similarity_threshold: float,
         fallback_threshold: float,
         queryaware_threshold: float,
+        heads: Optional[Sequence[int]] = None,
+        vpool: Optional[torch.Tensor] = None,
+        spool: Optional[torch.Tensor] = None,
     ):
         """Selection from pooled scores (attention_sharing.py:169-364).
 
         Returns ``(block_sets, use_dense, info)``: per head a sorted unique int64
         tensor of flat block indices ``row*nb+col``, a bool ``[H]`` marking heads
         elected pivot in this layer, and a dict of intermediates.
+
+        ``heads`` (with ``vpool``/``spool`` ``[H,nb]`` for ALL heads): the rows of
+        ``vertical``/``slash`` then belong to these heads only.  The election is replayed
+        over all heads; budgets and block sets are only meaningful for ``heads`` (the
+        other entries of the returned list are ``None``).
         """
-        h, n = vertical.shape
+        n = vertical.shape[-1]
         nb = -(-n // block_size)
         max_blocks = min(max_blocks, nb)
         nv, ns = block_budgets(vertical, slash, block_size, pattern_threshold, min_blocks, max_blocks)
-        vpool = block_sum_pool(vertical, block_size)
-        spool = block_sum_pool(slash, block_size)
+        if heads is None:
+            vpool = block_sum_pool(vertical, block_size)
+            spool = block_sum_pool(slash, block_size)
+        else:
+            idx = torch.as_tensor(list(heads))
+            nv_all = torch.full((avg_qk.shape[0],), min_blocks, dtype=nv.dtype)
+            ns_all = nv_all.clone()
+            nv_all[idx], ns_all[idx] = nv, ns
+            nv, ns = nv_all, ns_all
+        h = avg_qk.shape[0]
         jsd_qa = sqrt_jsd(avg_qk, vpool)
         use_qa = jsd_qa < queryaware_threshold
         use_dense = torch.zeros(h, dtype=torch.bool)
@@ -340,11 +356,13 @@ class SharingOracle:
 
         thr_sum = pattern_threshold * nb
         for hh in range(h):
-            if not bool(use_qa[hh]):
+            if not bool(use_qa[hh]) or (heads is not None and hh not in heads):
                 continue
             sc = qa_scores[hh] if isinstance(qa_scores, dict) else qa_scores(hh)
             sets[hh] = torch.unique(torch.cat((sets[hh], cover_indices_global(sc, thr_sum))))
 
+        if heads is not None:
+            sets = [s_ if hh in heads else None for hh, s_ in enumerate(sets)]
         info = dict(nv=nv, ns=ns, vpool=vpool, spool=spool, jsd_qa=jsd_qa, use_qa=use_qa,
                     use_share=use_share, jsd_v=jsd_v, jsd_s=jsd_s, vs_sets=vs_sets)
         return sets, use_dense, info
@@ -453,6 +471,35 @@ def sparse_attention(q, k, v, block_sets: Sequence[torch.Tensor], use_dense, bs:
                     avg[hh][r, c] = p.sum() / float(r1 - r0)
             o[r0:r1, hh, :] = (acc * torch.exp2(m_i - lse)[:, None]).to(q.dtype)
     return o, avg
+
+
+def pivot_block_mass(q_h: torch.Tensor, k_h: torch.Tensor, bs: int, scale: Optional[float] = None) -> torch.Tensor:
+    """Block-mass matrix ``[nb,nb]`` of one head that visits the full causal triangle: entry
+    (r, c) is the mean over query block r's rows of the softmax mass landing in key block c
+    (shareprefill_attn.py:425-457).  Same quantity as the ``use_dense`` pass of
+    ``sparse_attention``, computed a query block at a time (one matrix product per row block)
+    so that 32K- and 128K-token pivots finish in seconds; the row normaliser is a direct
+    log-sum-exp instead of the online one (equal up to fp32 rounding).  ``q_h``/``k_h`` ``[N,D]``."""
+    n, d = q_h.shape
+    nb = -(-n // bs)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    qk_scale = scale * math.log2(math.e)
+    qf, kf = q_h.float(), k_h.float()
+    out = torch.zeros(nb, nb, dtype=torch.float32)
+    pos = torch.arange(n)
+    for r in range(nb):
+        r0, r1 = r * bs, min((r + 1) * bs, n)
+        s = (qf[r0:r1] @ kf[:r1].T) * qk_scale
+        s = s.masked_fill(pos[r0:r1, None] < pos[None, :r1], float("-inf"))
+        m = s.max(dim=1, keepdim=True).values
+        lse = m + torch.log2(torch.exp2(s - m).sum(dim=1, keepdim=True))
+        p = torch.exp2(s - lse).sum(dim=0)
+        pad = (r + 1) * bs - r1
+        if pad:
+            p = torch.nn.functional.pad(p, (0, pad))
+        out[r, :r + 1] = p.view(r + 1, bs).sum(-1) / float(r1 - r0)
+    return out
 
 
 def masked_dense_attention(q, k, v, block_sets, bs: int, scale: Optional[float] = None):

@@ -69,3 +69,59 @@ class GoldenCase:
             return {}
         a = self.t(f"L{layer}_avg_attn")
         return {h: a[i] for i, h in enumerate(heads)}
+
+
+# ----------------------------------------------------------------------------- benchmark-sized cases
+SCALE_CASE_NAMES = ["qa_8k", "mixed_8k", "qwen_8k", "llama_32k", "llama_32k_diffuse", "group_128k"]
+
+
+def shipped_lookup_path():
+    from shareprefill_b200.configuration import SharePrefillConfig
+    return SharePrefillConfig(model_name="Llama-3.1-8B-Instruct").sharing_lookup_path
+
+
+def bitmap_to_sets_cpu(bm: torch.Tensor, nb: int):
+    """uint32-as-int64 ``[H][nb][nbw]`` -> per-head sorted flat indices ``row*nb+col``."""
+    h, _, nbw = bm.shape
+    bits = (bm.to(torch.int64).unsqueeze(-1) >> torch.arange(32)) & 1
+    dense = bits.reshape(h, nb, nbw * 32)[:, :, :nb].bool()
+    return [torch.nonzero(dense[i].reshape(-1)).flatten() for i in range(h)]
+
+
+class ScaleCase(GoldenCase):
+    """A case at a benchmark configuration's size: the reference's results for every head and its
+    un-pooled scores for ``score_heads`` (see make_golden.py, SCALE_CASES)."""
+
+    def __init__(self, name):
+        super().__init__(name)
+        meta = json.loads(str(self.z["meta"]))
+        self.layers = meta["layers"]
+        self.score_heads = meta["score_heads"]
+        self.all_scores = self.score_heads == list(range(self.wl.num_q_heads))
+        if self.lookup == "shipped":
+            from shareprefill_b200.sharing_state import load_lookup
+            clusters, shared = load_lookup(shipped_lookup_path())
+            self.lookup = {"clusters": clusters, "shared_clusters": sorted(shared)}
+            self.lookup_file = shipped_lookup_path()
+        else:
+            self.lookup_file = None
+
+    def bitmap(self, layer):
+        """int64 tensor holding the uint32 words ``[H][nb][nbw]``."""
+        return torch.from_numpy(self.z[f"L{layer}_bitmap"].astype(np.int64))
+
+    def bitmap_i32(self, layer):
+        return torch.from_numpy(self.z[f"L{layer}_bitmap"].view(np.int32))
+
+    def sets(self, layer):
+        return bitmap_to_sets_cpu(self.bitmap(layer), self.nb)
+
+    def qa_scores(self, layer):
+        heads = self.z[f"L{layer}_qa_score_heads"].tolist()
+        if not heads:
+            return {}
+        sc = self.t(f"L{layer}_qa_scores")
+        return {h: sc[i] for i, h in enumerate(heads)}
+
+    def shared_ids(self):
+        return [str(c) for c in self.z["shared_ids"].tolist()]
