@@ -15,8 +15,15 @@ dominant kernel (block-sparse attention, tensor bound) and ``roofline_pool`` for
 kernel (HBM bound); ``cpu_baseline`` = the CPU oracle timed on a bounded sample of the same
 workload and extrapolated to a full step.
 
-``--impl reference`` times the reference's algorithm on the host cores only (the CPU oracle,
-a port: the reference's Triton kernels cannot run on a CPU), same metric and config.
+At N = 1 the line also carries, measured after the timed region on ONE layer of the workload:
+``incumbent`` = the unmodified reference (its torch selection + Triton kernels, from baseline/_ref)
+and torch's dense causal SDPA on the same inputs next to this path; ``sparse_regime`` = one layer
+with the queries scaled by 4 (a few percent of the causal blocks visited).
+
+``--impl reference`` times the reference's algorithm on the host cores only: the reference's own
+selection code (from baseline/_ref, run on CPU) where it is installed, else its port, plus the
+port of the attention kernel (the reference's Triton kernels cannot run on a CPU); same metric and
+config, CPU_THREADS host threads in every arm.
 With N > 1 (torchrun) heads are sharded by KV group; total work is fixed (strong scaling).
 """
 from __future__ import annotations
@@ -40,10 +47,22 @@ from shareprefill_b200.workloads import WORKLOADS, AttentionWorkload, make_qkv, 
 
 STAGES = ["pool", "profile", "select", "attention", "pivot_update"]
 DISTINCT_LAYER_INPUTS = 4   # host/device inputs are drawn for this many layers and cycled
-# DRAM bytes (read + write) of ONE launch of the block-sparse attention kernel, from ncu captures of
-# these workloads on one GPU (profiles/sparse_attn_tc5_cfg1_and_cfg2.md); None where not captured
-ATTENTION_DRAM_BYTES_PER_LAUNCH = {("cfg2", 131072, 1.0): 3039617280 + 1056879104,
-                                   ("cfg1", 32768, 1.0): 403427072 + 234135296}
+# host threads of the CPU legs (cpu_baseline, --impl reference): fixed, so that one GPU and a
+# torchrun launch (which sets OMP_NUM_THREADS=1) divide by the same denominator
+CPU_THREADS = min(16, os.cpu_count() or 1)
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def ncu_dram_bytes(kernel: str, wl) -> "int | None":
+    """DRAM bytes (read + write) of ONE launch of ``kernel`` on this workload, from the ncu captures
+    tabulated in profiles/ncu_dram_bytes.json; None where that workload was not captured."""
+    path = os.path.join(ROOT, "profiles", "ncu_dram_bytes.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        table = json.load(f).get(kernel, {})
+    e = table.get(f"{wl.num_q_heads}q{wl.num_kv_heads}kv:{wl.seq_len}:{wl.q_gain:g}")
+    return None if e is None else int(e["dram_read_bytes"]) + int(e["dram_write_bytes"])
 
 
 def measured_peaks():
@@ -139,27 +158,48 @@ def config_dict(wl: AttentionWorkload, n_gpus: int):
 
 # ------------------------------------------------------------------------------ CPU arm
 def cpu_sample(wl: AttentionWorkload, rows_per_head: int = 3, seed_layer: int = 0):
-    """Time the CPU oracle on one layer, one KV group of the workload: selection in full,
-    attention on a few query-block rows per head; extrapolate to a full step."""
+    """Time the reference's CPU path on one layer, one KV group of the workload: selection in full
+    (the reference's own get_active_blocks from baseline/_ref where installed, else its port),
+    attention (port) on a few query-block rows per head; extrapolate to a full step."""
     from oracle import spf_oracle as orc
+    torch.set_num_threads(CPU_THREADS)
     g = wl.group_size
     sub = wl.replace(num_q_heads=g, num_kv_heads=1)
     q, k, v = make_qkv(sub, seed_layer, dtype=torch.bfloat16)
     lookup = synthetic_lookup(1, g, 1, shared=[])
-    st = orc.SharingOracle(lookup)
     bs, nb = wl.block_size, wl.num_blocks
-    t0 = time.perf_counter()
-    sets, use_dense, _ = st.get_active_blocks(
-        q, k, 0, block_size=bs, min_blocks=math.ceil(wl.min_budget / bs),
-        max_blocks=2**31 - 1, pattern_threshold=wl.pattern_threshold,
-        similarity_threshold=wl.similarity_threshold, fallback_threshold=wl.fallback_threshold,
-        queryaware_threshold=wl.queryaware_threshold)
-    t_sel = time.perf_counter() - t0
+    kn = dict(block_size=bs, min_blocks=math.ceil(wl.min_budget / bs), max_blocks=2**31 - 1,
+              pattern_threshold=wl.pattern_threshold, similarity_threshold=wl.similarity_threshold,
+              fallback_threshold=wl.fallback_threshold, queryaware_threshold=wl.queryaware_threshold)
+    kind = "port"
+    att = None
+    try:
+        from oracle.reference_shim import import_reference_selection, reference_get_active_blocks
+        att = import_reference_selection(REF_DIR)
+    except Exception:  # noqa: BLE001 - not installed, or its imports fail on this box: time the port
+        att = None
+    if att is not None:
+        with tempfile.NamedTemporaryFile("w", suffix=".json", delete=False) as f:
+            json.dump(lookup, f)
+        ref_state = att.AttentionSharing(f.name)
+        os.remove(f.name)
+        t0 = time.perf_counter()
+        block_idx, dense = reference_get_active_blocks(
+            att, ref_state, q, k, 0, g, bs, kn["min_blocks"], kn["max_blocks"], kn["pattern_threshold"],
+            kn["similarity_threshold"], kn["fallback_threshold"], kn["queryaware_threshold"])
+        t_sel = time.perf_counter() - t0
+        sets, use_dense = [block_idx[0][h].to(torch.int64) for h in range(g)], dense[0]
+        kind = "ref-selection+port-attention"
+    else:
+        st = orc.SharingOracle(lookup)
+        t0 = time.perf_counter()
+        sets, use_dense, _ = st.get_active_blocks(q, k, 0, **kn)
+        t_sel = time.perf_counter() - t0
     rows = sorted({nb - 1, nb // 2, nb // 5, 1}.__iter__())[-rows_per_head:]
-    visited_total = sum(len(s) for s in sets)
+    visited_total = sum(len(s_) for s_ in sets)
     sampled = 0
-    for s in sets:
-        r = torch.div(s, nb, rounding_mode="floor")
+    for s_ in sets:
+        r = torch.div(s_, nb, rounding_mode="floor")
         sampled += int(sum((r == x).sum() for x in rows))
     t0 = time.perf_counter()
     orc.sparse_attention(q, k, v, sets, use_dense, bs, rows=rows)
@@ -167,16 +207,18 @@ def cpu_sample(wl: AttentionWorkload, rows_per_head: int = 3, seed_layer: int = 
     groups = wl.num_kv_heads
     per_layer = t_sel * groups + t_attn * (visited_total / max(sampled, 1)) * groups
     return dict(ms_per_step=per_layer * wl.num_layers * 1e3, t_select_s=t_sel, t_attn_sample_s=t_attn,
-                sampled_blocks=sampled, visited_blocks_group=visited_total,
-                sample=f"1 layer, 1 KV group ({g} query heads) of the workload: selection in full, attention on "
-                       f"query-block rows {rows} ({sampled} of {visited_total} visited blocks), scaled by "
-                       f"visited blocks x {groups} groups x {wl.num_layers} layers (extrapolated)")
+                sampled_blocks=sampled, visited_blocks_group=visited_total, kind=kind,
+                sample=f"1 layer, 1 KV group ({g} query heads) of the workload on {CPU_THREADS} host threads: "
+                       f"selection in full ({'the reference code' if att is not None else 'port'}), attention "
+                       f"(port) on query-block rows {rows} ({sampled} of {visited_total} visited blocks), "
+                       f"scaled by visited blocks x {groups} groups x {wl.num_layers} layers (extrapolated)")
 
 
 def run_reference_arm(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    torch.set_num_threads(CPU_THREADS)
     cores = torch.get_num_threads()
     vals = []
     for i in range(args.warmup + args.steps):
@@ -188,26 +230,26 @@ def run_reference_arm(args, wl):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": config_dict(wl, args.gpus),
-            "cpu_baseline": {"value": ms, "unit": "ms", "cores": cores, "kind": "port", "sample": vals[-1]["sample"]},
+            "cpu_baseline": {"value": ms, "unit": "ms", "cores": cores, "kind": vals[-1]["kind"],
+                             "sample": vals[-1]["sample"]},
             "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
 
 
 # ------------------------------------------------------------------------------ reference on the GPU
-def run_reference_triton_arm(args, wl):
-    """Informational arm: the UNMODIFIED reference (its torch selection code and Triton kernels, from
-    the offline install under baseline/_ref) on the same GPU and the same inputs, one GPU only.
-    Not the contract's reference arm (that one is the CPU port); it shows the incumbent GPU path."""
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref_dir, "shareprefill")):
-        print(json.dumps({"impl": "reference-triton", "unavailable": "baseline/_ref is not installed"}))
-        return
-    sys.path.insert(0, ref_dir)
-    from shareprefill.attn import shareprefill_attn as ref_attn
-    from shareprefill.attn.attention_sharing import AttentionSharing as RefSharing
-    dev = torch.device("cuda:0")
-    torch.cuda.set_device(dev)
+def _reference_gpu_modules(wl):
+    """The UNMODIFIED reference from baseline/_ref: (AttentionSharing instance, attention module), or a
+    string saying why it cannot run."""
+    if not os.path.isdir(os.path.join(REF_DIR, "shareprefill")):
+        return "baseline/_ref is not installed"
+    if REF_DIR not in sys.path:
+        sys.path.insert(0, REF_DIR)
+    try:
+        from shareprefill.attn import shareprefill_attn as ref_attn
+        from shareprefill.attn.attention_sharing import AttentionSharing as RefSharing
+    except Exception as e:  # noqa: BLE001
+        return f"the reference does not import here: {type(e).__name__}: {e}"
     lookup_path = workload_lookup(wl)
     if lookup_path.endswith("_table.json"):      # the reference reads its own JSON layout only
         from shareprefill_b200.clusters.convert_lookup import from_table
@@ -217,9 +259,42 @@ def run_reference_triton_arm(args, wl):
         json.dump(lk, tmp)
         tmp.close()
         lookup_path = tmp.name
-    sharing = RefSharing(lookup_path)
-    L, nd, g = wl.num_layers, min(DISTINCT_LAYER_INPUTS, wl.num_layers), wl.group_size
+    return RefSharing(lookup_path), ref_attn
+
+
+def _reference_gpu_layer(sharing, ref_attn, wl, q, k, v, layer, stage=None):
+    """One layer through the reference's own entry points (attn/attention_sharing.py:105-366,
+    attn/shareprefill_attn.py:474-620); q/k/v are [1,N,H,D] with K/V already repeated."""
     bs = wl.block_size
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    ev[0].record()
+    block_idx, use_dense = sharing.get_active_blocks(
+        q, k, layer, wl.num_q_heads, bs, math.ceil(wl.min_budget / bs), 2**31 - 1,
+        wl.pattern_threshold, wl.similarity_threshold, wl.fallback_threshold, wl.queryaware_threshold, False)
+    ev[1].record()
+    o, avg = ref_attn.triton_block_wise_prefill_attention(q, k, v, block_idx, use_dense, bs)
+    ev[2].record()
+    sharing.update_pivotal_attns(layer, avg, use_dense, wl.pattern_threshold)
+    ev[3].record()
+    if stage is not None:
+        torch.cuda.synchronize()
+        for name, a, b in (("select", 0, 1), ("attention", 1, 2), ("pivot_update", 2, 3)):
+            stage[name] += ev[a].elapsed_time(ev[b])
+    return o
+
+
+def run_reference_triton_arm(args, wl):
+    """Informational arm: the UNMODIFIED reference (its torch selection code and Triton kernels, from
+    the offline install under baseline/_ref) on the same GPU and the same inputs, one GPU only.
+    Not the contract's reference arm (that one runs on the host cores); it shows the incumbent GPU path."""
+    mods = _reference_gpu_modules(wl)
+    if isinstance(mods, str):
+        print(json.dumps({"impl": "reference-triton", "unavailable": mods}))
+        return
+    sharing, ref_attn = mods
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    L, nd, g = wl.num_layers, min(DISTINCT_LAYER_INPUTS, wl.num_layers), wl.group_size
     inputs = []
     for i in range(nd):
         q, k, v = make_qkv(wl, i, device="cuda")
@@ -231,20 +306,7 @@ def run_reference_triton_arm(args, wl):
         sharing.reset_state()
         for layer in range(L):
             q, k, v = inputs[layer % nd]
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-            ev[0].record()
-            block_idx, use_dense = sharing.get_active_blocks(
-                q, k, layer, wl.num_q_heads, bs, math.ceil(wl.min_budget / bs), 2**31 - 1,
-                wl.pattern_threshold, wl.similarity_threshold, wl.fallback_threshold, wl.queryaware_threshold, False)
-            ev[1].record()
-            o, avg = ref_attn.triton_block_wise_prefill_attention(q, k, v, block_idx, use_dense, bs)
-            ev[2].record()
-            sharing.update_pivotal_attns(layer, avg, use_dense, wl.pattern_threshold)
-            ev[3].record()
-            if record:
-                torch.cuda.synchronize()
-                for name, a, b in (("select", 0, 1), ("attention", 1, 2), ("pivot_update", 2, 3)):
-                    stage[name] += ev[a].elapsed_time(ev[b])
+            _reference_gpu_layer(sharing, ref_attn, wl, q, k, v, layer, stage if record else None)
 
     for _ in range(args.warmup):
         step(False)
@@ -260,6 +322,111 @@ def run_reference_triton_arm(args, wl):
                       "config": config_dict(wl, 1), "stage_ms": {k_: v_ / args.steps for k_, v_ in stage.items()},
                       "note": "K/V repeated to the query-head count as the reference's entry point does; the repeat "
                               "and the [B,N,H,D] copies it makes are outside this timing"}))
+
+
+def _event_ms(fn, warmup=1, reps=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def one_layer_ours(wl, q, k, v, lookup_path, cfg, reps=3):
+    """One layer of this path on resident inputs: (ms, per-stage ms, visited blocks, visited fraction)."""
+    from shareprefill_b200 import native
+    from shareprefill_b200.attention import sparse_prefill_attention
+    from shareprefill_b200.sharing_state import AttentionSharing
+    sharing = AttentionSharing(lookup_path)
+    scale = 1.0 / math.sqrt(wl.head_dim)
+    marks = []
+
+    def run():
+        sharing.reset_state()
+        return sparse_prefill_attention(sharing, q, k, v, 0, wl.num_q_heads, cfg, scale)
+
+    ms = _event_ms(run, 2, reps)
+    sharing.on_stage = lambda name: marks.append((name, _recorded_event()))
+    marks.append(("begin", _recorded_event()))
+    _, pat = run()
+    torch.cuda.synchronize()
+    sharing.on_stage = None
+    stage = {n1: e0.elapsed_time(e1) for (_, e0), (n1, e1) in zip(marks[:-1], marks[1:])}
+    blocks = int(native.bitmap_row_counts(pat.bitmap)[1].sum())
+    tri = wl.num_blocks * (wl.num_blocks + 1) // 2
+    return ms, stage, blocks, blocks / (tri * wl.num_q_heads)
+
+
+def _recorded_event():
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    return ev
+
+
+def measure_incumbents(wl, lookup_path, cfg, peaks):
+    """After the timed region, one GPU, ONE layer of the workload on the same inputs: this path, the
+    unmodified reference (torch selection + Triton kernels) and torch's dense causal SDPA; then one
+    layer of the sparse regime (queries scaled by 4)."""
+    q, k, v = make_qkv(wl, 0, device="cuda")
+    ours_ms, ours_stage, blocks, frac = one_layer_ours(wl, q, k, v, lookup_path, cfg)
+    inc = {"workload": f"one layer of {wl.name} (N={wl.seq_len}, layer-0 inputs), 1 warm-up + 3 timed passes, CUDA events",
+           "ours_ms_per_layer": ours_ms, "ours_stage_ms": ours_stage, "ours_visited_fraction": frac}
+    # dense causal attention of the library (every causal block, no selection)
+    import torch.nn.functional as F
+    qh, kh, vh = (t.transpose(0, 1)[None] for t in (q, k, v))
+    backend = "torch default"
+
+    def dense():
+        return F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, enable_gqa=wl.group_size > 1)
+
+    try:
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        with sdpa_kernel(SDPBackend.CUDNN_ATTENTION):
+            dense_ms = _event_ms(dense)
+        backend = "cuDNN"
+    except Exception:  # noqa: BLE001 - that backend refuses the shape here: let torch choose
+        torch.cuda.synchronize()
+        dense_ms = _event_ms(dense)
+    tri = wl.num_blocks * (wl.num_blocks + 1) // 2
+    dense_flops = tri * wl.num_q_heads * 4.0 * wl.block_size ** 2 * wl.head_dim
+    inc.update(dense_sdpa_ms_per_layer=dense_ms, dense_sdpa_backend=backend,
+               dense_sdpa_tflops=dense_flops / dense_ms / 1e9)
+    # the unmodified reference on the same GPU
+    mods = _reference_gpu_modules(wl)
+    if isinstance(mods, str):
+        inc["triton_reference"] = {"unavailable": mods}
+    else:
+        sharing, ref_attn = mods
+        g = wl.group_size
+        rq, rk, rv = (q[None].contiguous(), k.repeat_interleave(g, dim=1)[None].contiguous(),
+                      v.repeat_interleave(g, dim=1)[None].contiguous())
+        try:
+            sharing.reset_state()
+            _reference_gpu_layer(sharing, ref_attn, wl, rq, rk, rv, 0)        # warm-up (Triton JIT)
+            stage = {"select": 0.0, "attention": 0.0, "pivot_update": 0.0}
+            for _ in range(3):
+                sharing.reset_state()
+                _reference_gpu_layer(sharing, ref_attn, wl, rq, rk, rv, 0, stage)
+            stage = {k_: v_ / 3 for k_, v_ in stage.items()}
+            inc["triton_reference"] = {"ms_per_layer": sum(stage.values()), "stage_ms": stage}
+        except Exception as e:  # noqa: BLE001
+            inc["triton_reference"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        del rq, rk, rv
+    del q, k, v, qh, kh, vh
+    torch.cuda.empty_cache()
+    # sparse regime: queries x4
+    wl4 = wl.replace(q_gain=4.0)
+    q, k, v = make_qkv(wl4, 0, device="cuda")
+    ms4, stage4, blocks4, frac4 = one_layer_ours(wl4, q, k, v, lookup_path, cfg)
+    tf4 = blocks4 * 4.0 * wl.block_size ** 2 * wl.head_dim / (stage4["attention"] / 1e3) / 1e12
+    sparse = {"q_gain": 4, "ms_per_layer": ms4, "stage_ms": stage4, "visited": frac4, "tflops": tf4,
+              "frac": tf4 / peaks["tflops"], "of": peaks["source"]}
+    return inc, sparse
 
 
 # ------------------------------------------------------------------------------ GPU arm
@@ -447,10 +614,18 @@ def run_gpu_arm(args, wl):
             dist.destroy_process_group()
         return
 
+    timeouts = native.load().spf_device_timeouts()
+    if timeouts:
+        raise SystemExit(f"{timeouts} bounded device-side waits gave up during the run: results are invalid")
+    incumbent = sparse = None
+    if world == 1 and not args.no_incumbents:
+        del dev_in, stage_bufs, out_bufs, host_in, host_out
+        torch.cuda.empty_cache()
+        incumbent, sparse = measure_incumbents(wl, lookup_path, cfg, peaks)
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         c = cpu_sample(wl)
-        cpu = {"value": c["ms_per_step"], "unit": "ms", "cores": torch.get_num_threads(), "kind": "port",
+        cpu = {"value": c["ms_per_step"], "unit": "ms", "cores": torch.get_num_threads(), "kind": c["kind"],
                "sample": c["sample"]}
     line = {
         "metric": "sparse_prefill_attention_ms_per_forward", "value": ms_step, "unit": "ms",
@@ -462,18 +637,21 @@ def run_gpu_arm(args, wl):
         "stage_ms_rank0": stage_ms, "host_issue_ms_per_step": host_issue_ms,
         "roofline": {"kernel": "block-sparse attention", "bound": "tensor", "achieved": achieved_tf,
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved_tf / peaks["tflops"],
-                     "traffic": ATTENTION_DRAM_BYTES_PER_LAUNCH.get((wl.name, wl.seq_len, wl.q_gain)) if world == 1 else None,
+                     "traffic": ncu_dram_bytes("sparse_attn_tc5_kernel", wl) if world == 1 else None,
                      "traffic_unit": "bytes per launch (ncu dram read+write)", "of": peaks["source"]},
         "roofline_pool": {"kernel": "Q/K block pooling", "bound": "hbm", "achieved": pool_gbs,
                           "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": pool_gbs / peaks["hbm_gbs"],
-                          "traffic": {131072: 1342209280 + 10450176, 32768: 335595008 + 6505472}.get(wl.seq_len)
-                          if (world == 1 and wl.num_q_heads == 32 and wl.num_kv_heads == 8) else None,
+                          "traffic": ncu_dram_bytes("pool_blocks_kernel", wl) if world == 1 else None,
                           "traffic_unit": "bytes per launch (ncu dram read+write)", "of": peaks["source"]},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
         "gpu_launches": launches_timed,
+        "device_timeouts": timeouts,
         "clocks": clocks,
     }
+    if incumbent is not None:
+        line["incumbent"] = incumbent
+        line["sparse_regime"] = sparse
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -490,6 +668,8 @@ def main():
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--q-gain", type=float, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-incumbents", action="store_true",
+                    help="skip the one-layer reference / dense SDPA / sparse-regime measurements (N=1)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.layers:
@@ -505,6 +685,14 @@ def main():
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the sparse-prefill kernels have no CPU fallback")
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        if wl.num_kv_heads % world:
+            # heads shard by whole KV groups only: splitting a group would duplicate its K/V
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"unavailable": f"{wl.name} has {wl.num_kv_heads} KV heads: it shards over at most "
+                                                 f"{wl.num_kv_heads} GPUs by whole KV groups, not over {world}",
+                                  "n_gpus": world, "config": config_dict(wl, world)}))
+            return
         run_gpu_arm(args, wl)
 
 

@@ -41,7 +41,9 @@ typedef enum spf_status {
   SPF_ERR_ALIGN = -3,       /* pointer or stride not 16-byte aligned */
   SPF_ERR_RANGE = -4,       /* argument out of range (thresholds, budgets, layer, slots) */
   SPF_ERR_LAUNCH = -5,      /* CUDA reported an error at launch; see spf_last_cuda_error */
-  SPF_ERR_TOO_LARGE = -6    /* size beyond a compiled-in maximum */
+  SPF_ERR_TOO_LARGE = -6,   /* size beyond a compiled-in maximum */
+  SPF_ERR_TIMEOUT = -7      /* bounded device-side waits gave up earlier in this process; the tcgen05
+                               kernels refuse to run until spf_reset_device_timeouts() */
 } spf_status;
 
 /* head flag bits written by spf_elect_and_share */
@@ -248,10 +250,31 @@ int spf_decode_attention(const void* q, int64_t q_stride_h,
                          double softmax_scale, void* out, void* scratch, int64_t scratch_bytes,
                          void* stream);
 
-/* Number of bounded device-side waits that gave up since the library was loaded (0 in a
- * healthy run).  The tcgen05 kernel never spins without a limit: a wait that runs out makes
- * its CTA drain and return, and is counted here.  Synchronises the device. */
+/* ---------------------------------------------------------------- bounded device-side waits
+ * The tcgen05 kernels never spin without a limit: a wait (on an mbarrier) that has been spinning for
+ * longer than the wait limit makes its CTA drain and return - its rows of the output stay unwritten -
+ * and is counted.  The reference has no counterpart (its Triton kernels have no such waits); the
+ * caller is expected to read the counter at a point where a device synchronisation is cheap (the
+ * Python host does so at the start of every forward and raises).
+ *   spf_device_timeouts        waits that gave up since the library was loaded or the counter was
+ *                              reset (0 in a healthy run).  Synchronises the device.  Once it has
+ *                              returned more than 16, spf_sparse_attention and spf_lastblock_profile
+ *                              return SPF_ERR_TIMEOUT instead of launching.
+ *   spf_reset_device_timeouts  zero the counter (after the caller has dealt with the event).
+ *   spf_set_device_wait_limit_ns  the limit, default 1e9 ns; time during which the CTA was not
+ *                              running is not counted.  Meant for tests.
+ *   spf_wait_limit_selftest    launches one tiny kernel whose only wait can never complete: it returns
+ *                              after the limit and the counter goes up by one.  Meant for tests. */
 int spf_device_timeouts(void);
+int spf_reset_device_timeouts(void);
+int spf_set_device_wait_limit_ns(uint64_t ns);
+int spf_wait_limit_selftest(void* stream);
+
+/* Test hook (no counterpart in the reference): two kernels serve block_size = head_dim = 128 - the
+ * tcgen05 ones and the mma.sync ones that also cover every other shape.  A non-zero `attention` /
+ * `profile` makes spf_sparse_attention / spf_lastblock_profile take the mma.sync kernel from now on,
+ * so that a test can run both on the same inputs.  Process-wide; deployments never call it. */
+int spf_force_generic_kernels(int attention, int profile);
 
 /* ---------------------------------------------------------------- pivot update
  * For every head elected pivot in this layer: per-row cumulative-mass cover of its

@@ -1,4 +1,5 @@
 // C ABI of libspf_b200.so: argument validation and dispatch.  See include/spf_b200.h.
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -7,6 +8,12 @@
 
 namespace spf {
 static thread_local cudaError_t g_last_error = cudaSuccess;
+// the value spf_device_timeouts() last returned: lets a launcher refuse work without a synchronisation
+static std::atomic<unsigned int> g_known_timeouts{0};
+static inline bool timeouts_tripped() { return g_known_timeouts.load(std::memory_order_relaxed) > 16u; }
+// test hooks (spf_force_generic_kernels): run the mma.sync kernels where the tcgen05 ones would
+static std::atomic<int> g_force_generic_attention{0}, g_force_generic_profile{0};
+bool force_generic_profile() { return g_force_generic_profile.load(std::memory_order_relaxed) != 0; }
 void note_cuda_error(cudaError_t e) { g_last_error = e; }
 
 static inline bool strides_ok(int64_t sn, int64_t sh) { return (sn % 8 == 0) && (sh % 8 == 0); }
@@ -26,6 +33,7 @@ const char* spf_status_string(int status) {
     case SPF_ERR_RANGE: return "argument out of range";
     case SPF_ERR_LAUNCH: return "CUDA launch error (see spf_last_cuda_error)";
     case SPF_ERR_TOO_LARGE: return "size beyond a compiled-in maximum";
+    case SPF_ERR_TIMEOUT: return "bounded device-side waits gave up earlier (spf_device_timeouts); reset with spf_reset_device_timeouts";
     default: return "unknown status";
   }
 }
@@ -79,6 +87,7 @@ int spf_lastblock_profile(const void* q, int64_t q_stride_n, int64_t q_stride_h,
                           int n_kv_heads, int head_dim, int block_size, float* vertical, float* slash,
                           void* scratch, int64_t scratch_bytes, void* stream) {
   if (!q || !k || !vertical || !slash || !scratch) return SPF_ERR_NULL;
+  if (timeouts_tripped()) return SPF_ERR_TIMEOUT;
   int rc = check_shape(n_tokens, n_q_heads, n_kv_heads, head_dim, block_size);
   if (rc) return rc;
   if (!aligned16(q) || !aligned16(k) || !aligned16(scratch) || !strides_ok(q_stride_n, q_stride_h) ||
@@ -243,6 +252,7 @@ int spf_sparse_attention(const void* q, int64_t q_stride_n, int64_t q_stride_h, 
                          const uint32_t* bitmap, const int32_t* head_flags, const int32_t* slot_of_head,
                          void* state, int n_slots, void* out, void* stream) {
   if (!q || !k || !v || !bitmap || !out) return SPF_ERR_NULL;
+  if (timeouts_tripped()) return SPF_ERR_TIMEOUT;
   int rc = check_shape(n_tokens, n_q_heads, n_kv_heads, head_dim, block_size);
   if (rc) return rc;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !strides_ok(q_stride_n, q_stride_h) ||
@@ -263,10 +273,10 @@ int spf_sparse_attention(const void* q, int64_t q_stride_n, int64_t q_stride_h, 
   p.pivot_only = 0;
   p.n_slots = with_state ? n_slots : 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // block_size = head_dim = 128 runs on the tcgen05 kernel; SPF_ATTENTION_KERNEL=generic (a test
-  // hook) keeps the mma.sync kernel, which also serves every other supported shape
-  const char* force = std::getenv("SPF_ATTENTION_KERNEL");
-  const bool want_tc5 = block_size == 128 && head_dim == 128 && !(force && std::strcmp(force, "generic") == 0);
+  // block_size = head_dim = 128 runs on the tcgen05 kernel; spf_force_generic_kernels (a test hook)
+  // keeps the mma.sync kernel, which also serves every other supported shape
+  const bool want_tc5 = block_size == 128 && head_dim == 128 &&
+                        g_force_generic_attention.load(std::memory_order_relaxed) == 0;
   if (want_tc5) {
     rc = sparse_attention_tc5(p, n_kv_heads, st);
     if (rc == SPF_OK) {
@@ -321,7 +331,30 @@ int spf_decode_attention(const void* q, int64_t q_stride_h, const void* k, int64
   return decode_attention(p, head_dim, static_cast<cudaStream_t>(stream));
 }
 
-int spf_device_timeouts(void) { return static_cast<int>(tc5_timeout_count() + est_tc5_timeout_count()); }
+int spf_device_timeouts(void) {
+  const unsigned int n = tc5_timeout_count() + est_tc5_timeout_count();
+  g_known_timeouts.store(n, std::memory_order_relaxed);
+  return static_cast<int>(n);
+}
+
+int spf_reset_device_timeouts(void) {
+  if (!tc5_reset_timeouts() || !est_tc5_reset_timeouts()) return SPF_ERR_LAUNCH;
+  g_known_timeouts.store(0, std::memory_order_relaxed);
+  return SPF_OK;
+}
+
+int spf_set_device_wait_limit_ns(uint64_t ns) {
+  if (ns == 0) return SPF_ERR_RANGE;
+  return (tc5_set_wait_limit(ns) && est_tc5_set_wait_limit(ns)) ? SPF_OK : SPF_ERR_LAUNCH;
+}
+
+int spf_force_generic_kernels(int attention, int profile) {
+  g_force_generic_attention.store(attention ? 1 : 0, std::memory_order_relaxed);
+  g_force_generic_profile.store(profile ? 1 : 0, std::memory_order_relaxed);
+  return SPF_OK;
+}
+
+int spf_wait_limit_selftest(void* stream) { return tc5_wait_limit_selftest(static_cast<cudaStream_t>(stream)); }
 
 int spf_update_pivots(const int32_t* head_flags, const int32_t* slot_of_head, void* state, int n_slots, int n_heads,
                       int nb, double pattern_threshold, void* stream) {

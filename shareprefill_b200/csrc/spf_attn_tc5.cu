@@ -39,6 +39,14 @@ constexpr uint32_t TC_SMEM_K = TC_SMEM_Q + 2 * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_V = TC_SMEM_K + TC_KSTAGES * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_V + TC_VSTAGES * TC_TILE_BYTES;   // 225 KiB of the 227 KiB limit
 constexpr float TC_RESCALE_LOG2 = 8.0f;
+// of every 8 element pairs of a score row, this many get their exponential from the FMA-pipe polynomial
+#ifndef TC5_POLY_PAIRS
+#define TC5_POLY_PAIRS 0
+#endif
+// 1: one elected lane per softmax warp arrives on the "P ready" barrier (4 arrivals) instead of every thread (128)
+#ifndef TC5_WARP_ARRIVE
+#define TC5_WARP_ARRIVE 0
+#endif
 
 // Timing probe, compiled in only with -DSPF_TC5_TRACE: clock64() stamps of the first CTA's
 // first 64 iterations, [role: softmax A, softmax B, MMA issuer][iteration][slot].
@@ -128,7 +136,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(bar_q, 1);
     for (int s = 0; s < TC_KSTAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_kempty(s), 2); }
     for (int s = 0; s < TC_VSTAGES; ++s) { mbar_init(bar_vfull(s), 1); mbar_init(bar_vempty(s), 2); }
-    for (int h = 0; h < 2; ++h) { mbar_init(bar_sfull(h), 1); mbar_init(bar_pready(h), 128); mbar_init(bar_odone(h), 1); }
+    for (int h = 0; h < 2; ++h) { mbar_init(bar_sfull(h), 1); mbar_init(bar_pready(h), TC5_WARP_ARRIVE ? 4 : 128); mbar_init(bar_odone(h), 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -361,6 +369,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         const float mx = fmaxf(fmaxf(row_max(s0), row_max(s1)), fmaxf(row_max(s2), row_max(s3)));
         const float mb = mx * p.scale_log2;
+        if (lane == 0 && quarter == 0) TRACE(h, k, 5);
         float alpha = 1.f;
         bool grow = false;
         if (k == 0) {
@@ -385,15 +394,21 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // P = 2^(s*scale - m) as bf16 over the first 64 columns of the S region
         float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
         uint32_t pk[16];
-        exp_pack(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tS + 0, pk);
-        exp_pack(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tS + 16, pk);
-        exp_pack(s2, p.scale_log2, m_used, pk, l2); tmem_st16(tS + 32, pk);
-        exp_pack(s3, p.scale_log2, m_used, pk, l3); tmem_st16(tS + 48, pk);
+        exp_pack_mixed<TC5_POLY_PAIRS>(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tS + 0, pk);
+        exp_pack_mixed<TC5_POLY_PAIRS>(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tS + 16, pk);
+        exp_pack_mixed<TC5_POLY_PAIRS>(s2, p.scale_log2, m_used, pk, l2); tmem_st16(tS + 32, pk);
+        exp_pack_mixed<TC5_POLY_PAIRS>(s3, p.scale_log2, m_used, pk, l3); tmem_st16(tS + 48, pk);
         l_sum += (l0 + l1) + (l2 + l3);
         if (lane == 0 && quarter == 0) TRACE(h, k, 3);
         tc_wait_st();
+        if (lane == 0 && quarter == 0) TRACE(h, k, 6);
         tc_fence_before();
+#if TC5_WARP_ARRIVE
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_pready(h));
+#else
         mbar_arrive(bar_pready(h));
+#endif
         if (lane == 0 && quarter == 0) TRACE(h, k, 4);
       }
       // ---- epilogue
@@ -463,10 +478,27 @@ int sparse_attention_tc5(const AttnParams& a, int n_kv_heads, cudaStream_t st) {
 extern "C" void spf_tc5_trace_dump(long long* out) { cudaMemcpyFromSymbol(out, g_tc5_trace, sizeof(long long) * 3 * 64 * 8); }
 #endif
 
-unsigned int tc5_timeout_count() {
-  unsigned int v = 0;
-  cudaMemcpyFromSymbol(&v, g_tc5_timeouts, sizeof(v));
-  return v;
+unsigned int tc5_timeout_count() { return tc5_read_timeouts_here(); }
+bool tc5_reset_timeouts() { return tc5_reset_timeouts_here(); }
+bool tc5_set_wait_limit(unsigned long long ns) { return tc5_set_wait_limit_here(ns); }
+
+// Self-test of the bounded wait: one thread waits on an mbarrier that nothing ever arrives on.  The
+// wait runs out after the configured limit, the event is counted and the kernel returns normally.
+__global__ void wait_limit_probe_kernel() {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_addr(&bar), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(smem_addr(&bar), 0, &abort_flag);
+  __syncthreads();
+}
+int tc5_wait_limit_selftest(cudaStream_t st) {
+  wait_limit_probe_kernel<<<1, 32, 0, st>>>();
+  return check_launch();
 }
 
 }  // namespace spf

@@ -297,10 +297,9 @@ int lastblock_profile(const EstParams& p, int head_dim, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(p.slash, 0, sizeof(float) * int64_t(p.n_q_heads) * p.n_tokens, st);
   if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
   if (head_dim == 128) {
-    // tcgen05 kernels unless SPF_PROFILE_KERNEL=generic asks for the mma.sync ones (used by the tests
+    // tcgen05 kernels unless spf_force_generic_kernels asks for the mma.sync ones (used by the tests
     // to compare the two) or the key tensor cannot be described to TMA
-    const char* force = std::getenv("SPF_PROFILE_KERNEL");
-    if (!(force && std::strcmp(force, "generic") == 0)) {
+    if (!force_generic_profile()) {
       const int rc = lastblock_profile_tc5(p, st);
       if (rc != SPF_ERR_SHAPE) return rc;
     }

@@ -377,10 +377,8 @@ int lastblock_profile_tc5(const EstParams& e, cudaStream_t st) {
   return check_launch();
 }
 
-unsigned int est_tc5_timeout_count() {
-  unsigned int v = 0;
-  cudaMemcpyFromSymbol(&v, g_tc5_timeouts, sizeof(v));
-  return v;
-}
+unsigned int est_tc5_timeout_count() { return tc5_read_timeouts_here(); }
+bool est_tc5_reset_timeouts() { return tc5_reset_timeouts_here(); }
+bool est_tc5_set_wait_limit(unsigned long long ns) { return tc5_set_wait_limit_here(ns); }
 
 }  // namespace spf

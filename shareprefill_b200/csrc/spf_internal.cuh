@@ -120,10 +120,16 @@ struct DecodeParams {
 
 int decode_attention(const DecodeParams& p, int head_dim, cudaStream_t st);
 int lastblock_profile_tc5(const EstParams& p, cudaStream_t st);
+bool force_generic_profile();
 unsigned int est_tc5_timeout_count();
+bool est_tc5_reset_timeouts();
+bool est_tc5_set_wait_limit(unsigned long long ns);
 int sparse_attention_generic(const AttnParams& p, int block_size, int head_dim, cudaStream_t st);
 int sparse_attention_tc5(const AttnParams& p, int n_kv_heads, cudaStream_t st);
 unsigned int tc5_timeout_count();
+bool tc5_reset_timeouts();
+bool tc5_set_wait_limit(unsigned long long ns);
+int tc5_wait_limit_selftest(cudaStream_t st);
 int lastblock_profile(const EstParams& p, int head_dim, cudaStream_t st);
 int pool_blocks(const PoolParams& p, int nb, cudaStream_t st);
 int launch_budgets(const BudgetParams& p, cudaStream_t st);

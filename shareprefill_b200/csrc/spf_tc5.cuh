@@ -18,6 +18,8 @@ constexpr uint32_t TC_SLAB_BYTES = TC_TILE_BYTES / 2;       // [128 rows][64 ele
 
 // bounded device-side waits that gave up (read back by the host after a run)
 static __device__ unsigned int g_tc5_timeouts = 0;
+// how long a wait may spin before it gives up (1 s; tests shorten it)
+static __constant__ unsigned long long c_tc5_wait_limit_ns = 1000000000ull;
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
@@ -46,17 +48,23 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false once the CTA has aborted (unless `drain`) or after ~1 s without completion.
+// Bounded wait: false once the CTA has aborted (unless `drain`) or after the wait limit has been spent
+// SPINNING.  Time is added up between consecutive looks at the clock and a single gap counts for at
+// most 1 ms, so a CTA that was not running for a while (a time slice taken by another context, a
+// profiler replay) is not mistaken for one that hangs.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           bool drain = false) {
   if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
+  unsigned long long last = global_ns(), spent = 0;
   int spins = 0;
   while (true) {
     if (mbar_try(bar, parity)) return true;
     if ((++spins & 63) == 0) {
       if (*abort_flag && !drain) return false;
-      if (global_ns() - t0 > 1000000000ull) {
+      const unsigned long long now = global_ns(), gap = now - last;
+      last = now;
+      spent += gap < 1000000ull ? gap : 1000000ull;
+      if (spent > c_tc5_wait_limit_ns) {
         *abort_flag = 1;
         atomicAdd(&g_tc5_timeouts, 1u);
         return false;
@@ -118,7 +126,6 @@ __device__ __forceinline__ float row_max(const uint32_t (&r)[32]) {
   }
   return max3(fmaxf(a, b), __uint_as_float(r[30]), __uint_as_float(r[31]));
 }
-__device__ __forceinline__ float fast_exp2(float x);
 // two fp32 lanes in one 64-bit register (packed fp32x2 arithmetic of sm_100)
 __device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
   unsigned long long d;
@@ -155,6 +162,53 @@ __device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], float scale, f
     float y0, y1;
     f2_unpack(f2_fma(x, sc2, nm2), y0, y1);
     const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+    acc[(j >> 1) & 3] = f2_add(acc[(j >> 1) & 3], f2_pack(p0, p1));
+    pk[j >> 1] = bf16x2_from(p0, p1);
+  }
+  float a0, a1;
+  f2_unpack(f2_add(f2_add(acc[0], acc[1]), f2_add(acc[2], acc[3])), a0, a1);
+  sum += a0 + a1;
+}
+
+// The same with POLY of every 8 element pairs taken off the exponential unit: their 2^x comes from a
+// Cody-Waite range reduction and a degree-3 polynomial on the FMA pipe (relative error 7.5e-5, far
+// below the bf16 rounding of P), so the MUFU sees (8 - POLY)/8 of the exponentials.
+//   u = sat((x + 120) / 128) in [0,1]            x = s*scale - m is at most 2^8 above zero; below -120 -> 2^-120
+//   n = round(128u - 120) by the 1.5*2^23 trick; f = 128u - 120 - n in [-0.5, 0.5]
+//   2^x = p(f) * 2^n: n is added to the exponent field of p(f)
+template <int POLY>
+__device__ __forceinline__ void exp_pack_mixed(const uint32_t (&r)[32], float scale, float m, uint32_t (&pk)[16], float& sum) {
+  const unsigned long long sc2 = f2_pack(scale, scale), nm2 = f2_pack(-m, -m);
+  const float sc128 = scale * 0.0078125f, b128 = (120.f - m) * 0.0078125f;
+  constexpr float MAGIC = 12582912.f - 120.f;      // 1.5 * 2^23 - 120
+  const unsigned long long k128 = f2_pack(128.f, 128.f), kmag = f2_pack(MAGIC, MAGIC), kneg = f2_pack(-1.f, -1.f);
+  const unsigned long long c0 = f2_pack(0.99992806f, 0.99992806f), c1 = f2_pack(0.69326097f, 0.69326097f),
+                           c2 = f2_pack(0.24261113f, 0.24261113f), c3 = f2_pack(0.05517167f, 0.05517167f);
+  unsigned long long acc[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    float p0, p1;
+    if (((j >> 1) & 7) < POLY) {
+      const float u0 = __saturatef(fmaf(__uint_as_float(r[j]), sc128, b128));
+      const float u1 = __saturatef(fmaf(__uint_as_float(r[j + 1]), sc128, b128));
+      const unsigned long long u = f2_pack(u0, u1);
+      const unsigned long long xf = f2_fma(u, k128, kmag);          // MAGIC + n (n in the low mantissa bits)
+      const unsigned long long c = f2_fma(xf, kneg, kmag);          // -(120 + n)
+      const unsigned long long f = f2_fma(u, k128, c);
+      unsigned long long pl = f2_fma(f, c3, c2);
+      pl = f2_fma(pl, f, c1);
+      pl = f2_fma(pl, f, c0);
+      float q0, q1, x0, x1;
+      f2_unpack(pl, q0, q1);
+      f2_unpack(xf, x0, x1);
+      p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(x0) << 23));
+      p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(x1) << 23));
+    } else {
+      const unsigned long long x = f2_pack(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+      float y0, y1;
+      f2_unpack(f2_fma(x, sc2, nm2), y0, y1);
+      p0 = fast_exp2(y0); p1 = fast_exp2(y1);
+    }
     acc[(j >> 1) & 3] = f2_add(acc[(j >> 1) & 3], f2_pack(p0, p1));
     pk[j >> 1] = bf16x2_from(p0, p1);
   }
@@ -305,6 +359,20 @@ static bool make_map(CUtensorMap* m, const void* base, int n_tokens, int heads, 
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// the counter and the wait limit exist once per translation unit that includes this header
+static unsigned int tc5_read_timeouts_here() {
+  unsigned int v = 0;
+  cudaMemcpyFromSymbol(&v, g_tc5_timeouts, sizeof(v));
+  return v;
+}
+static bool tc5_reset_timeouts_here() {
+  const unsigned int z = 0;
+  return cudaMemcpyToSymbol(g_tc5_timeouts, &z, sizeof(z)) == cudaSuccess;
+}
+static bool tc5_set_wait_limit_here(unsigned long long ns) {
+  return cudaMemcpyToSymbol(c_tc5_wait_limit_ns, &ns, sizeof(ns)) == cudaSuccess;
 }
 
 }  // namespace spf

@@ -54,6 +54,10 @@ SIGNATURES = {
     "spf_sparse_attention": (_I, [_P, _L, _L, _P, _L, _L, _P, _L, _L, _I, _I, _I, _I, _I, _D, _P, _P, _P,
                                   _P, _I, _P, _P]),
     "spf_device_timeouts": (_I, []),
+    "spf_reset_device_timeouts": (_I, []),
+    "spf_set_device_wait_limit_ns": (_I, [C.c_uint64]),
+    "spf_wait_limit_selftest": (_I, [_P]),
+    "spf_force_generic_kernels": (_I, [_I, _I]),
     "spf_pivot_summary_width": (_L, [_I]),
     "spf_pack_pivot_summaries": (_I, [_P, _I, _I, _I, _I, _I, _P, _P]),
     "spf_merge_pivot_summaries": (_I, [_P, _I, _I, _P, _I, _P]),
@@ -93,6 +97,24 @@ def _check(rc: int, what: str):
         if rc == -5:
             msg += ": " + lib.spf_last_cuda_error().decode()
         raise SpfError(f"{what} failed ({rc}): {msg}")
+
+
+def device_timeouts() -> int:
+    """Bounded device-side waits that gave up since the last reset (synchronises the device)."""
+    return int(load().spf_device_timeouts())
+
+
+def raise_on_device_timeouts() -> None:
+    """Raise if a tcgen05 kernel gave up on a wait since the last check: the rows its CTA owned were
+    never written, so whatever was computed since is not to be trusted.  The counter is cleared, so
+    the next forward starts clean.  Costs one device synchronisation."""
+    if _lib is None:
+        return
+    n = int(_lib.spf_device_timeouts())
+    if n:
+        _lib.spf_reset_device_timeouts()
+        raise SpfError(f"{n} bounded device-side wait(s) gave up in a tcgen05 kernel since the last check: "
+                       "the outputs of that forward are incomplete")
 
 
 def _stream() -> int:

@@ -1,6 +1,7 @@
 """``SharePrefill(...)(model)``: patch a Hugging Face decoder-only model in place.
 
-Mirrors shareprefill_patch.py:31-169: registers the attention function under the name
+Mirrors shareprefill_patch.py:31-169 of opas-lab/SharePrefill (Apache-2.0; the argument list, the
+side effects and the error messages of that file are this boundary's contract): registers the attention function under the name
 ``"shareprefill"`` in the modeling module's ``ALL_ATTENTION_FUNCTIONS``, sets
 ``config._attn_implementation``, installs ``_init_attention_sharing`` /
 ``reset_attention_sharing`` on the model class, copies the knobs onto ``model.config`` at
@@ -18,6 +19,7 @@ import functools
 import importlib
 import logging
 
+from . import native
 from .attention import shareprefill_attention_forward
 from .configuration import SharePrefillConfig
 from .sharing_state import AttentionSharing
@@ -103,6 +105,9 @@ def shareprefill_patch(model, config: SharePrefillConfig):
 
     @functools.wraps(original)
     def forward_with_reset(self, *args, **kwargs):
+        # a kernel of the previous forward that gave up on a bounded wait left rows unwritten: say so
+        # here, where a synchronisation costs nothing (the previous forward's result has been used)
+        native.raise_on_device_timeouts()
         self.reset_attention_sharing()
         return original(self, *args, **kwargs)
 

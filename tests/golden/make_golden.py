@@ -32,7 +32,6 @@ profiles) and its un-pooled score tensors only for the heads listed in ``score_h
 from __future__ import annotations
 
 import argparse
-import contextlib
 import hashlib
 import json
 import math
@@ -47,6 +46,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 
 from oracle import spf_oracle as orc  # noqa: E402
+from oracle.reference_shim import cuda_string_to_cpu  # noqa: E402
 from shareprefill_b200.workloads import AttentionWorkload, make_qkv, synthetic_lookup  # noqa: E402
 
 
@@ -55,28 +55,6 @@ def tensor_digest(*ts) -> str:
     for t in ts:
         hsh.update(t.contiguous().view(torch.uint8).numpy().tobytes())
     return hsh.hexdigest()
-
-
-@contextlib.contextmanager
-def cuda_string_to_cpu():
-    real_empty, real_to = torch.empty, torch.Tensor.to
-
-    def empty(*a, **kw):
-        if kw.get("device") == "cuda":
-            kw["device"] = "cpu"
-        return real_empty(*a, **kw)
-
-    def to(self, *a, **kw):
-        a = tuple("cpu" if (isinstance(x, str) and x == "cuda") else x for x in a)
-        if kw.get("device") == "cuda":
-            kw["device"] = "cpu"
-        return real_to(self, *a, **kw)
-
-    torch.empty, torch.Tensor.to = empty, to
-    try:
-        yield
-    finally:
-        torch.empty, torch.Tensor.to = real_empty, real_to
 
 
 CASES = {

@@ -125,3 +125,23 @@ class ScaleCase(GoldenCase):
 
     def shared_ids(self):
         return [str(c) for c in self.z["shared_ids"].tolist()]
+
+
+def same_cover_up_to_ties(got: torch.Tensor, want: torch.Tensor, scores: torch.Tensor) -> bool:
+    """Are two selections of one head (bool ``[nb*nb]``) the same cumulative-mass cover of ``scores``
+    (fp32 ``[nb*nb]``)?  The reference keeps a prefix of ``torch.sort(descending=True)``; several blocks
+    may share the score at which the running sum crosses the threshold (equal bf16 logits in one
+    softmax row give equal fp32 scores), and torch's default sort leaves the order of equal values
+    open - on CPU it is not index order.  So two covers are the same selection when they hold equally
+    many blocks and differ only among blocks whose score is that one crossing value."""
+    diff = got ^ want
+    if not bool(diff.any()):
+        return True
+    vals = scores[diff]
+    return int(got.sum()) == int(want.sum()) and bool((vals == vals[0]).all())
+
+
+def bitmap_row_bools(bm_words: torch.Tensor, nb: int) -> torch.Tensor:
+    """int32/int64 words ``[nb][nbw]`` of one head -> bool ``[nb*nb]``."""
+    bits = (bm_words.to(torch.int64).unsqueeze(-1) >> torch.arange(32)) & 1
+    return bits.reshape(nb, -1)[:, :nb].bool().reshape(-1)

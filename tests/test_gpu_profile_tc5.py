@@ -1,6 +1,5 @@
 """Last-block profile: the tcgen05 kernels (head_dim 128) against the CPU oracle and against the
 mma.sync kernels on the same inputs."""
-import os
 
 import pytest
 import torch
@@ -12,19 +11,13 @@ pytestmark = pytest.mark.gpu
 
 
 def _profile(q, k, bs, kernel):
-    old = os.environ.get("SPF_PROFILE_KERNEL")
-    if kernel == "generic":
-        os.environ["SPF_PROFILE_KERNEL"] = "generic"
-    else:
-        os.environ.pop("SPF_PROFILE_KERNEL", None)
+    lib = native.load()
+    lib.spf_force_generic_kernels(0, 1 if kernel == "generic" else 0)
     try:
         v, s = native.lastblock_profile(q, k, bs)
         torch.cuda.synchronize()
     finally:
-        if old is None:
-            os.environ.pop("SPF_PROFILE_KERNEL", None)
-        else:
-            os.environ["SPF_PROFILE_KERNEL"] = old
+        lib.spf_force_generic_kernels(0, 0)
     return v, s
 
 

@@ -10,7 +10,8 @@ import numpy as np
 import pytest
 import torch
 
-from golden_cases import GOLDEN_DIR, SCALE_CASE_NAMES, ScaleCase
+from golden_cases import (GOLDEN_DIR, SCALE_CASE_NAMES, ScaleCase, bitmap_row_bools,
+                          same_cover_up_to_ties)
 from oracle import spf_oracle as orc
 from shareprefill_b200 import native
 from shareprefill_b200.sharing_state import AttentionSharing
@@ -80,7 +81,10 @@ def test_budgets_and_pooled_profiles_from_reference_profiles(dev, name):
 @pytest.mark.parametrize("name", SCALE_CASE_NAMES)
 def test_block_sets_from_reference_scores_are_exact(dev, name, tmp_path_factory):
     """Fed the reference's recorded scores, the device selection returns the reference's block sets,
-    flags, pivots, shared pattern and vs_ratio bit for bit (for the heads whose scores are kept)."""
+    flags, pivots, shared pattern and vs_ratio bit for bit (for the heads whose scores are kept).
+    One freedom exists: where several blocks of a query-aware head share the score at which the
+    cumulative mass crosses the threshold, torch's sort does not define which of them the reference
+    keeps; there the two sets must hold equally many blocks and differ only among those equal scores."""
     gc = ScaleCase(name)
     wl = gc.wl
     H, g = wl.num_q_heads, wl.group_size
@@ -90,7 +94,7 @@ def test_block_sets_from_reference_scores_are_exact(dev, name, tmp_path_factory)
     subset = not gc.all_scores
     sharing = AttentionSharing(path, head_range=(h0, h1) if subset else None)
     sharing.reset_state()
-    identical = 0
+    identical = tied = 0
     for layer in gc.layers:
         q, k, v = gc.qkv(layer)
         q, k = q[:, h0:h1].to(dev), k[:, h0 // g:h1 // g].to(dev)
@@ -109,9 +113,15 @@ def test_block_sets_from_reference_scores_are_exact(dev, name, tmp_path_factory)
         assert torch.equal((flags & native.HEAD_QUERY_AWARE) != 0, gc.t(f"L{layer}_use_qa")[h0:h1]), layer
         want = gc.bitmap_i32(layer)[h0:h1]
         got = pat.bitmap.cpu()
+        qa_sc = gc.qa_scores(layer)
         for h in range(h1 - h0):
-            assert torch.equal(got[h], want[h]), f"{name} layer {layer} head {h0 + h}: bitmaps differ"
-            identical += 1
+            if torch.equal(got[h], want[h]):
+                identical += 1
+                continue
+            assert (h0 + h) in qa_sc, f"{name} layer {layer} head {h0 + h}: bitmaps differ"
+            assert same_cover_up_to_ties(bitmap_row_bools(got[h], gc.nb), bitmap_row_bools(want[h], gc.nb),
+                                         qa_sc[h0 + h]), f"{name} layer {layer} head {h0 + h}: covers differ"
+            tied += 1
         # the pivot's block-mass matrix as the reference saw it, then the pattern update
         slots = pat.slot_of_head.tolist()
         if gc.has(f"L{layer}_avg_attn"):
@@ -129,7 +139,8 @@ def test_block_sets_from_reference_scores_are_exact(dev, name, tmp_path_factory)
         want_ratio = float(gc.z[f"S{cid}_vs_ratio"])
         if want_ratio == want_ratio:
             assert abs(float(st.field("vs_ratio")[slot]) - want_ratio) <= 1e-5 * abs(want_ratio)
-    _report(dict(test="sets_from_reference_scores", case=name, heads_checked=identical, heads_identical=identical))
+    _report(dict(test="sets_from_reference_scores", case=name, heads_checked=identical + tied,
+                 heads_identical=identical, heads_equal_up_to_tied_scores=tied))
 
 
 @pytest.mark.parametrize("name", SCALE_CASE_NAMES)
@@ -189,13 +200,23 @@ def test_from_qkv_at_scale(dev, name, tmp_path_factory):
 def test_query_aware_cover_with_tied_scores(dev, nb):
     """Scores that repeat, so the crossing value is shared by several blocks: both bodies of the cover
     kernel (16-byte loads at nb % 32 == 0 when no tie needs a rank, the ranking pass otherwise) against
-    the reference's score_cover_idx; equal values go lowest index first."""
+    the reference's score_cover_idx.  Same number of blocks, identical outside the crossing value
+    (which of the equal scores are kept is the sort's choice: the kernel takes the lowest indices)."""
     z = np.load(f"{GOLDEN_DIR}/qa_ties.npz")
     p = torch.from_numpy(z[f"tie{nb}_scores"])
     for thr in (0.5, 0.9, 0.95):
         bm = torch.zeros(1, nb, native.bitmap_words(nb), dtype=torch.int32, device=dev)
         native.query_aware_select(p[None].contiguous().to(dev), None, thr, bm)
-        got = native.bitmap_to_sets(bm)[0].cpu()
-        want = torch.from_numpy(z[f"tie{nb}_kept_{thr}"])
-        zero = torch.zeros(1, dtype=torch.int64)
-        assert torch.equal(torch.unique(torch.cat((got, zero))), torch.unique(torch.cat((want, zero)))), (nb, thr)
+        got = bitmap_row_bools(bm[0].cpu(), nb)
+        want = torch.zeros(nb * nb, dtype=torch.bool)
+        want[torch.from_numpy(z[f"tie{nb}_kept_{thr}"])] = True
+        got[0] = want[0] = True          # the reference pads with index 0
+        assert same_cover_up_to_ties(got, want, p.reshape(-1)), (nb, thr)
+        # lowest index first among the equal scores
+        diff = got ^ want
+        if bool(diff.any()):
+            v = p.reshape(-1)[diff][0]
+            tied = torch.nonzero(p.reshape(-1) == v).flatten()
+            kept = got[tied]
+            n_kept = int(kept.sum())
+            assert bool(kept[:n_kept].all()) and not bool(kept[n_kept:].any())

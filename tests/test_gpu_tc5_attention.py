@@ -1,7 +1,6 @@
 """The tcgen05/TMEM attention kernel (block_size = head_dim = 128) against the CPU oracle and
 against the generic mma.sync kernel on the same inputs."""
 import math
-import os
 
 import pytest
 import torch
@@ -35,19 +34,13 @@ def _random_sets(nb, h, density, g):
 
 
 def _run(q, k, v, bm, kernel):
-    old = os.environ.get("SPF_ATTENTION_KERNEL")
-    if kernel == "generic":
-        os.environ["SPF_ATTENTION_KERNEL"] = "generic"
-    else:
-        os.environ.pop("SPF_ATTENTION_KERNEL", None)
+    lib = native.load()
+    lib.spf_force_generic_kernels(1 if kernel == "generic" else 0, 0)
     try:
         out = native.sparse_attention(q, k, v, bm, 128, 1.0 / math.sqrt(128))
         torch.cuda.synchronize()
     finally:
-        if old is None:
-            os.environ.pop("SPF_ATTENTION_KERNEL", None)
-        else:
-            os.environ["SPF_ATTENTION_KERNEL"] = old
+        lib.spf_force_generic_kernels(0, 0)
     return out
 
 
@@ -83,8 +76,8 @@ def test_tc5_matches_oracle_and_generic(n, h, hkv, density):
     (4096, 8, 8, 1.0),       # single-head items, dense
 ])
 def test_tc5_many_items_per_cta_matches_generic(n, h, hkv, density):
-    """More work items than SMs: every persistent CTA runs several items back to back, so the
-    rings, the Q buffer and the TMEM accumulators are handed from one item to the next."""
+    """Many more (query block, head pair) items than SMs: several waves of CTAs, rows of very
+    different lengths, both issue modes (heads of a pair that visit the same or different blocks)."""
     dev = torch.device("cuda:0")
     g = torch.Generator().manual_seed(n + 3 * h)
     q = torch.randn(n, h, 128, generator=g).bfloat16().to(dev)
@@ -98,7 +91,7 @@ def test_tc5_many_items_per_cta_matches_generic(n, h, hkv, density):
     m[2, 7] = False
     sets = [torch.nonzero(m[i].reshape(-1)).flatten() for i in range(h)]
     bm = native.sets_to_bitmap(sets, nb, dev)
-    for _ in range(2):       # twice: the second launch draws from a fresh work counter
+    for _ in range(2):       # twice: a second launch right behind the first
         out_tc5 = _run(q, k, v, bm, "tc5")
         assert native.load().spf_device_timeouts() == 0, "a bounded wait in the tcgen05 kernel ran out"
     out_gen = _run(q, k, v, bm, "generic")
