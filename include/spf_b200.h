@@ -173,6 +173,12 @@ int spf_elect_and_share(const float* jsd_qa_all, const int32_t* slot_of_head_all
                         double fallback_threshold, int min_blocks,
                         int32_t* nv, int32_t* ns, int32_t* head_flags, void* stream);
 
+/* Offline head clustering (no counterpart in the reference, which ships a finished lookup file but
+ * not the program that made it): out[i][j] = sqrt Jensen-Shannon divergence of x[i] and x[j], the
+ * measure of attn/utils.py:26-30, for n_vec fp32 distributions of length len (<= 2 * SPF_MAX_BLOCKS);
+ * out is fp32 [n_vec][n_vec].  Used by shareprefill_b200.clusters.build_lookup. */
+int spf_pairwise_sqrt_jsd(const float* x, int n_vec, int len, float* out, void* stream);
+
 /* ---------------------------------------------------------------- pattern bitmap
  * spf_build_vs_bitmap: top-k vertical columns / slash distances with the forced sink and
  * diagonal blocks, expanded to blocks, unioned with the full triangle (pivot) or the

@@ -179,6 +179,12 @@ int spf_classify_heads(const float* avg_qk, const float* vpool, const float* spo
   return launch_classify(p, n_heads, static_cast<cudaStream_t>(stream));
 }
 
+int spf_pairwise_sqrt_jsd(const float* x, int n_vec, int len, float* out, void* stream) {
+  if (!x || !out) return SPF_ERR_NULL;
+  if (n_vec <= 0 || n_vec > 65535 || len <= 0 || len > 2 * SPF_MAX_BLOCKS) return SPF_ERR_RANGE;
+  return launch_pairwise_jsd(x, n_vec, len, out, static_cast<cudaStream_t>(stream));
+}
+
 int spf_elect_and_share(const float* jsd_qa_all, const int32_t* slot_of_head_all, int n_heads_total,
                         int head_offset, int n_heads, const float* jsd_v, const float* jsd_s,
                         const float* vpool, const float* spool, void* state, int n_slots, int nb, int layer,

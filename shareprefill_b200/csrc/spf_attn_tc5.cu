@@ -30,14 +30,17 @@
 namespace spf {
 
 constexpr int TC_THREADS = 384;                             // 3 warpgroups: control, softmax A, softmax B
+constexpr int TC_REGS_CONTROL = 128, TC_REGS_SOFTMAX = 184; // setmaxnreg targets
+static_assert(4 * TC_REGS_CONTROL + 8 * TC_REGS_SOFTMAX <= 12 * 168, "setmaxnreg targets exceed the CTA's register pool");
 constexpr int TC_KSTAGES = 3;
 constexpr int TC_VSTAGES = 2;
-// shared memory map: 1 KiB of control data, then 1024-byte aligned tiles (Q x2, K x3, V x2)
+// shared memory map: 3 KiB of control data, then 1024-byte aligned tiles (Q x2, K x3, V x2)
 constexpr uint32_t TC_SMEM_CTRL = 0;                        // mbarriers, TMEM slot, abort flag
-constexpr uint32_t TC_SMEM_Q = 1024;
+constexpr uint32_t TC_SMEM_XCH = 1024;                      // [2 heads][128 rows][2] half-row sums of the two threads of a row
+constexpr uint32_t TC_SMEM_Q = 3072;
 constexpr uint32_t TC_SMEM_K = TC_SMEM_Q + 2 * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_V = TC_SMEM_K + TC_KSTAGES * TC_TILE_BYTES;
-constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_V + TC_VSTAGES * TC_TILE_BYTES;   // 225 KiB of the 227 KiB limit
+constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_V + TC_VSTAGES * TC_TILE_BYTES;   // 232448 bytes: the 227 KiB limit
 constexpr float TC_RESCALE_LOG2 = 8.0f;
 // of every 8 element pairs of a score row, this many get their exponential from the FMA-pipe polynomial
 #ifndef TC5_POLY_PAIRS
@@ -47,6 +50,26 @@ constexpr float TC_RESCALE_LOG2 = 8.0f;
 #ifndef TC5_WARP_ARRIVE
 #define TC5_WARP_ARRIVE 0
 #endif
+// 1: the row maximum is reduced element-wise across the four chunks first (short dependency chains)
+#ifndef TC5_MAX_TREE
+#define TC5_MAX_TREE 0
+#endif
+// 1: P is handed over in two parts (keys 0-95 as soon as they are written, then keys 96-127), so that
+// the first six k-steps of P V run under the last quarter of the exponentials
+#ifndef TC5_SPLIT_P
+#define TC5_SPLIT_P 0
+#endif
+// 1: all eight softmax warps work on ONE head's score tile at a time, two threads per query row (64 key
+// columns each), head A's tile then head B's: a softmax step takes half as long, which shortens the
+// chain softmax -> P V -> Q K^T -> softmax of a head, and the MMAs of one head run under the softmax of
+// the other.  0: a warpgroup per head, a thread per row.
+#ifndef TC5_PAIR_ROWS
+#define TC5_PAIR_ROWS 0
+#endif
+#if TC5_PAIR_ROWS && TC5_SPLIT_P
+#error "TC5_SPLIT_P is not implemented for TC5_PAIR_ROWS"
+#endif
+constexpr uint32_t TC_P_ARRIVALS = (TC5_WARP_ARRIVE ? 4u : 128u) * (TC5_PAIR_ROWS ? 2u : 1u);
 
 // Timing probe, compiled in only with -DSPF_TC5_TRACE: clock64() stamps of the first CTA's
 // first 64 iterations, [role: softmax A, softmax B, MMA issuer][iteration][slot].
@@ -115,8 +138,9 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   auto bar_sfull = [&](int h) { return bar0 + 8u * (11 + h); };
   auto bar_pready = [&](int h) { return bar0 + 8u * (13 + h); };
   auto bar_odone = [&](int h) { return bar0 + 8u * (15 + h); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_SMEM_CTRL + 8 * 17);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_SMEM_CTRL + 8 * 17 + 8);
+  auto bar_pearly = [&](int h) { return bar0 + 8u * (17 + h); };   // first three quarters of P written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_SMEM_CTRL + 8 * 19);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_SMEM_CTRL + 8 * 19 + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // CTAs that run at the same time belong to the same KV head (its K/V stream stays in L2);
@@ -136,7 +160,10 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     mbar_init(bar_q, 1);
     for (int s = 0; s < TC_KSTAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_kempty(s), 2); }
     for (int s = 0; s < TC_VSTAGES; ++s) { mbar_init(bar_vfull(s), 1); mbar_init(bar_vempty(s), 2); }
-    for (int h = 0; h < 2; ++h) { mbar_init(bar_sfull(h), 1); mbar_init(bar_pready(h), TC5_WARP_ARRIVE ? 4 : 128); mbar_init(bar_odone(h), 1); }
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(bar_sfull(h), 1); mbar_init(bar_odone(h), 1);
+      mbar_init(bar_pready(h), TC_P_ARRIVALS); mbar_init(bar_pearly(h), TC_P_ARRIVALS);
+    }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -150,8 +177,11 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t tmem = *tmem_slot;
 
   if (warp < 4) {
-    // control warpgroup (producer, MMA issuer, two idle warps) hands registers to the softmax warpgroups
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    // control warpgroup (producer, MMA issuers, an idle warp) hands registers to the softmax warpgroups.
+    // The CTA owns the registers it was launched with (384 threads x 168) and no more: 4 warps x 128 +
+    // 8 warps x 184 stays within that pool; a sum beyond it would leave the last setmaxnreg.inc waiting
+    // for ever.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_REGS_CONTROL));
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -231,17 +261,28 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // descriptors differ from a base only in the 14-bit address field: one 64-bit add per operand
       const uint64_t qdA = desc_kmajor(sbase + TC_SMEM_Q), qdB = desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES);
       const uint64_t kd0 = desc_kmajor(sbase + TC_SMEM_K), vd0 = desc_mnmajor(sbase + TC_SMEM_V);
-      auto issue_qk = [&](int h, int ks_stage) {
-        const uint64_t kd = kd0 + uint64_t((ks_stage * TC_TILE_BYTES) >> 4);
-        const uint64_t qd = h == 0 ? qdA : qdB;
-        const uint32_t ts = tmem + (h == 0 ? 0u : 128u);
-        mma_qk_group(ts, qd, kd);
-        tc_commit(bar_sfull(h));
-      };
-      auto issue_pv = [&](int h, int vs_stage, bool accumulate) {
-        const uint64_t vd = vd0 + uint64_t((vs_stage * TC_TILE_BYTES) >> 4);
+      // One head's share of an iteration: P V of the current block (if the head visits it) and Q K^T of
+      // the next one (if it visits that).  Everything that is not an MMA comes first - ring stages
+      // checked, the descriptors of all sixteen k-steps built - so that after the wait for P the
+      // instructions between the fence and the last MMA are MMAs only.
+      auto head_step = [&](int h, bool do_pv, bool do_qk, int vs_stage, int ks_stage, bool accumulate) {
+        KSteps vd, qd, kd;
+        if (do_pv) ksteps_mnmajor(vd0 + uint64_t((vs_stage * TC_TILE_BYTES) >> 4), vd);
+        if (do_qk) {
+          ksteps_kmajor(h == 0 ? qdA : qdB, qd);
+          ksteps_kmajor(kd0 + uint64_t((ks_stage * TC_TILE_BYTES) >> 4), kd);
+        }
         const uint32_t ts = tmem + (h == 0 ? 0u : 128u), to = tmem + (h == 0 ? 256u : 384u);
-        mma_pv_group(to, ts, vd, accumulate ? 1u : 0u);
+        // phase 0 (TC5_SPLIT_P only): the first six k-steps of P V; phase 1: the rest
+        return [=](int phase) {
+#if TC5_SPLIT_P
+          if (phase == 0) { if (do_pv) mma_pv_first6(to, ts, vd, accumulate ? 1u : 0u); return; }
+          if (do_pv) mma_pv_last2(to, ts, vd);
+#else
+          if (do_pv) mma_pv_x8(to, ts, vd, accumulate ? 1u : 0u);
+#endif
+          if (do_qk) { mma_qk_x8(ts, qd, kd); tc_commit(bar_sfull(h)); }
+        };
       };
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       PairWalker wk; wk.init(rowA, rowB, r);
@@ -255,7 +296,8 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ok = mbar_wait(bar_kfull(0), 0, abort_flag);
           tc_fence_after();
           if (ok) {
-            for (int h = 0; h < 2; ++h) if (fl & (1 << h)) issue_qk(h, 0);
+            for (int h = 0; h < 2; ++h)
+              if (fl & (1 << h)) head_step(h, false, true, 0, 0, false)(1);
             mbar_arrive(bar_kempty(0));
             tc_commit(bar_kempty(0));
           }
@@ -267,26 +309,33 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const int last_h = (fl & 2) ? 1 : 0;
           const int nlast_h = (nfl & 2) ? 1 : 0;
           for (int h = 0; h < 2 && ok; ++h) {
-            if (fl & (1 << h)) {
-              if (!v_ready) { ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
-              if (h == 0) TRACE(2, i, 0); else TRACE(2, i, 4);
-              if (ok) ok = mbar_wait(bar_pready(h), nblk[h] & 1, abort_flag);
+            const bool do_pv = (fl & (1 << h)) != 0;
+            const bool do_qk = ncol >= 0 && (nfl & (1 << h)) != 0;
+            if (!do_pv && !do_qk) continue;
+            if (do_pv && !v_ready) { ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
+            if (ok && do_qk && !nk_ready) { ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
+            if (!ok) break;
+            auto issue = head_step(h, do_pv, do_qk, vs, nks, nblk[h] > 0);
+            if (h == 0) TRACE(2, i, 0); else TRACE(2, i, 4);
+#if TC5_SPLIT_P
+            if (do_pv) {
+              ok = mbar_wait(bar_pearly(h), nblk[h] & 1, abort_flag);
               if (!ok) break;
               tc_fence_after();
-              if (h == 0) TRACE(2, i, 1); else TRACE(2, i, 5);
-              issue_pv(h, vs, nblk[h] > 0);
-              if (h == 0) TRACE(2, i, 2); else TRACE(2, i, 6);
+              issue(0);
+            }
+#endif
+            if (do_pv) ok = mbar_wait(bar_pready(h), nblk[h] & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            if (h == 0) TRACE(2, i, 1); else TRACE(2, i, 5);
+            issue(1);
+            if (h == 0) TRACE(2, i, 3); else TRACE(2, i, 7);
+            if (do_pv) {
               ++nblk[h];
               if (h == last_h) { mbar_arrive(bar_vempty(vs)); tc_commit(bar_vempty(vs)); }
             }
-            if (ncol >= 0 && (nfl & (1 << h))) {
-              if (!nk_ready) { ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
-              if (!ok) break;
-              tc_fence_after();
-              issue_qk(h, nks);
-              if (h == nlast_h) { mbar_arrive(bar_kempty(nks)); tc_commit(bar_kempty(nks)); }
-              if (h == 0) TRACE(2, i, 3); else TRACE(2, i, 7);
-            }
+            if (do_qk && h == nlast_h) { mbar_arrive(bar_kempty(nks)); tc_commit(bar_kempty(nks)); }
           }
           col = ncol; fl = nfl; ++i;
         }
@@ -299,31 +348,36 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok && col >= 0) {
           ok = mbar_wait(bar_kfull(0), 0, abort_flag);
           if (ok) {
-            if (fl & mine) { tc_fence_after(); issue_qk(h, 0); tc_commit(bar_kempty(0)); }
+            if (fl & mine) { tc_fence_after(); head_step(h, false, true, 0, 0, false)(1); tc_commit(bar_kempty(0)); }
             else mbar_arrive(bar_kempty(0));
           }
         }
         while (ok && col >= 0) {
           const int ncol = wk.next(nfl);
           const int vs = i % TC_VSTAGES, nks = (i + 1) % TC_KSTAGES;
+          const bool do_pv = (fl & mine) != 0, do_qk = ncol >= 0 && (nfl & mine) != 0;
           ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag);
+          if (ok && ncol >= 0) ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag);
           if (!ok) break;
-          if (fl & mine) {
-            ok = mbar_wait(bar_pready(h), np & 1, abort_flag);
+          if (do_pv || do_qk) {
+            auto issue = head_step(h, do_pv, do_qk, vs, nks, np > 0);
+#if TC5_SPLIT_P
+            if (do_pv) {
+              ok = mbar_wait(bar_pearly(h), np & 1, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              issue(0);
+            }
+#endif
+            if (do_pv) ok = mbar_wait(bar_pready(h), np & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            issue_pv(h, vs, np > 0);
-            ++np;
-            tc_commit(bar_vempty(vs));
-          } else {
-            mbar_arrive(bar_vempty(vs));
+            issue(1);
+            if (do_pv) ++np;
           }
-          if (ncol >= 0) {
-            ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag);
-            if (!ok) break;
-            if (nfl & mine) { tc_fence_after(); issue_qk(h, nks); tc_commit(bar_kempty(nks)); }
-            else mbar_arrive(bar_kempty(nks));
-          }
+          // a stage this head used is released when its MMAs are done, one it skipped at once
+          if (do_pv) tc_commit(bar_vempty(vs)); else mbar_arrive(bar_vempty(vs));
+          if (ncol >= 0) { if (do_qk) tc_commit(bar_kempty(nks)); else mbar_arrive(bar_kempty(nks)); }
           col = ncol; fl = nfl; ++i;
         }
         tc_commit(bar_odone(h));
@@ -332,7 +386,138 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
   } else {
     // ------------------------------------------------------------ softmax warpgroups
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TC_REGS_SOFTMAX));
+#if TC5_PAIR_ROWS
+    // ---- two threads per query row: warp 4+q and warp 8+q share the rows of TMEM lane quarter q (and
+    // scheduler q).  Both read the whole score row for its maximum - so they reach the same decisions
+    // without talking to each other - and `half` picks the 64 key columns whose exponentials, and the
+    // 64 output columns whose final scaling, this thread does.  The only value passed between the two
+    // is the half-row sum, left in shared memory before every hand-over of P and read once at the end.
+    const int half = (warp - 4) >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    float* xch = reinterpret_cast<float*>(smem + TC_SMEM_XCH);     // [2 heads][128 rows][2 halves]
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;  // reference point and half-row sum per head
+    int k_a = 0, k_b = 0;
+    bool ok = true;
+    {
+      PairWalker wk; wk.init(rowA, rowB, r);
+      int fl;
+      for (int col = wk.next(fl); col >= 0 && ok; col = wk.next(fl)) {
+        const bool diag = (col == r);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (!(fl & (1 << h)) || !ok) continue;
+          const int k = h == 0 ? k_a : k_b;
+          float m_used = h == 0 ? m_a : m_b;
+          float l_sum = h == 0 ? l_a : l_b;
+          const uint32_t tS = tmem + lane_base + uint32_t(h * 128);
+          const uint32_t tP = tmem + lane_base + uint32_t(h * 128 + half * 32);
+          const uint32_t tO = tmem + lane_base + uint32_t(256 + h * 128 + half * 64);
+          const bool tracer = lane == 0 && quarter == 0 && half == 0;
+          if (tracer) TRACE(h, k, 0);
+          ok = mbar_wait(bar_sfull(h), k & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          if (tracer) TRACE(h, k, 1);
+          // own half (kept for the exponentials) and the other half (only its maximum is needed)
+          uint32_t s0[32], s1[32], t0[32], t1[32];
+          tmem_ld32_raw(tS + uint32_t(half * 64), s0);
+          tmem_ld32_raw(tS + uint32_t(half * 64 + 32), s1);
+          tmem_ld32_raw(tS + uint32_t((half ^ 1) * 64), t0);
+          tmem_ld32_raw(tS + uint32_t((half ^ 1) * 64 + 32), t1);
+          tc_wait_ld();
+          if (tracer) TRACE(h, k, 2);
+          if (diag) {
+            mask_after(s0, row - half * 64);
+            mask_after(s1, row - half * 64 - 32);
+            mask_after(t0, row - (half ^ 1) * 64);
+            mask_after(t1, row - (half ^ 1) * 64 - 32);
+          }
+          const float mb = row_max4(s0, s1, t0, t1) * p.scale_log2;
+          if (tracer) TRACE(h, k, 5);
+          float alpha = 1.f;
+          bool grow = false;
+          if (k == 0) {
+            m_used = mb;
+          } else if (mb > m_used + TC_RESCALE_LOG2) {
+            alpha = exp2f(m_used - mb);
+            m_used = mb;
+            l_sum *= alpha;
+            grow = true;
+          }
+          if (__any_sync(0xffffffffu, grow)) {
+            // S_h(k) is complete, hence so is every earlier P V of this head: O_h is stable
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+              float v[32];
+              tmem_ld32(tO + c * 32, v);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] *= alpha;
+              tmem_st32(tO + c * 32, v);
+            }
+          }
+          float l0 = 0.f, l1 = 0.f;
+          uint32_t pk[16];
+          exp_pack_mixed<TC5_POLY_PAIRS>(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tP + 0, pk);
+          exp_pack_mixed<TC5_POLY_PAIRS>(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tP + 16, pk);
+          l_sum += l0 + l1;
+          xch[(h * 128 + row) * 2 + half] = l_sum;
+          if (tracer) TRACE(h, k, 3);
+          tc_wait_st();
+          if (tracer) TRACE(h, k, 6);
+          tc_fence_before();
+#if TC5_WARP_ARRIVE
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_pready(h));
+#else
+          mbar_arrive(bar_pready(h));
+#endif
+          if (tracer) TRACE(h, k, 4);
+          if (h == 0) { k_a = k + 1; m_a = m_used; l_a = l_sum; } else { k_b = k + 1; m_b = m_used; l_b = l_sum; }
+        }
+      }
+      // ---- epilogue: this thread writes 64 of the row's 128 output columns, per head
+      const int tok = row0 + row;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int head = h == 0 ? hA : hB;
+        if (head < 0 || !ok) continue;
+        const int k = h == 0 ? k_a : k_b;
+        const uint32_t tO = tmem + lane_base + uint32_t(256 + h * 128 + half * 64);
+        __nv_bfloat16* orow = p.out + (int64_t(tok) * p.n_q_heads + head) * TC_D + half * 64;
+        if (k > 0) ok = mbar_wait(bar_odone(h), 0, abort_flag);
+        if (!ok) continue;
+        tc_fence_after();
+        // the other half's sum was stored before that thread's last hand-over of P, which the last
+        // P V - and so this barrier - came after
+        const float l_row = k > 0 ? (h == 0 ? l_a : l_b) + xch[(h * 128 + row) * 2 + (half ^ 1)] : 0.f;
+        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          float v[32];
+          if (k > 0) {
+            tmem_ld32(tO + c * 32, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+          }
+          if (tok < p.n_tokens) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o;
+              o.x = pack2_bf16(v[j] * inv, v[j + 1] * inv);
+              o.y = pack2_bf16(v[j + 2] * inv, v[j + 3] * inv);
+              o.z = pack2_bf16(v[j + 4] * inv, v[j + 5] * inv);
+              o.w = pack2_bf16(v[j + 6] * inv, v[j + 7] * inv);
+              *reinterpret_cast<uint4*>(orow + c * 32 + j) = o;
+            }
+          }
+        }
+      }
+    }
+#else
     const int h = (warp - 4) >> 2;                 // 0: head A, 1: head B
     const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;           // query row within the block
@@ -367,7 +552,11 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mask_after(s2, row - 64);
           mask_after(s3, row - 96);
         }
+#if TC5_MAX_TREE
+        const float mx = row_max4(s0, s1, s2, s3);
+#else
         const float mx = fmaxf(fmaxf(row_max(s0), row_max(s1)), fmaxf(row_max(s2), row_max(s3)));
+#endif
         const float mb = mx * p.scale_log2;
         if (lane == 0 && quarter == 0) TRACE(h, k, 5);
         float alpha = 1.f;
@@ -397,6 +586,16 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         exp_pack_mixed<TC5_POLY_PAIRS>(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tS + 0, pk);
         exp_pack_mixed<TC5_POLY_PAIRS>(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tS + 16, pk);
         exp_pack_mixed<TC5_POLY_PAIRS>(s2, p.scale_log2, m_used, pk, l2); tmem_st16(tS + 32, pk);
+#if TC5_SPLIT_P
+        tc_wait_st();
+        tc_fence_before();
+#if TC5_WARP_ARRIVE
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_pearly(h));
+#else
+        mbar_arrive(bar_pearly(h));
+#endif
+#endif
         exp_pack_mixed<TC5_POLY_PAIRS>(s3, p.scale_log2, m_used, pk, l3); tmem_st16(tS + 48, pk);
         l_sum += (l0 + l1) + (l2 + l3);
         if (lane == 0 && quarter == 0) TRACE(h, k, 3);
@@ -441,6 +640,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
     }
+#endif  // TC5_PAIR_ROWS
   }
   __syncwarp();
   tc_fence_before();

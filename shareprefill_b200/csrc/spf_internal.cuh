@@ -135,6 +135,7 @@ int pool_blocks(const PoolParams& p, int nb, cudaStream_t st);
 int launch_budgets(const BudgetParams& p, cudaStream_t st);
 int launch_last_row(const LastRowParams& p, cudaStream_t st);
 int launch_classify(const ClassifyParams& p, int n_heads, cudaStream_t st);
+int launch_pairwise_jsd(const float* x, int n_vec, int len, float* out, cudaStream_t st);
 int launch_elect(const ElectParams& p, cudaStream_t st);
 int launch_vs_bitmap(const VsParams& p, int n_heads, cudaStream_t st);
 int launch_qa_scores(const QaScoreParams& p, cudaStream_t st);

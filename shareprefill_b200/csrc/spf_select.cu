@@ -133,6 +133,32 @@ __global__ void __launch_bounds__(256) classify_heads_kernel(const ClassifyParam
   if (threadIdx.x == 0) { p.jsd_qa[h] = jq; p.jsd_v[h] = jv; p.jsd_s[h] = js; }
 }
 
+// Pairwise divergence of n_vec distributions of length len (offline head clustering): out[i][j] =
+// sqrt-JSD(x_i, x_j), same arithmetic as block_sqrt_jsd.  grid (ceil(n_vec / 8), n_vec): a CTA holds row
+// i in shared memory and each of its eight warps takes one j.
+__global__ void __launch_bounds__(256) pairwise_sqrt_jsd_kernel(const float* x, int n_vec, int len, float* out) {
+  extern __shared__ float xi[];
+  const int i = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int t = threadIdx.x; t < len; t += blockDim.x) xi[t] = x[int64_t(i) * len + t];
+  __syncthreads();
+  const int j = blockIdx.x * 8 + warp;
+  if (j >= n_vec) return;
+  const float* xj = x + int64_t(j) * len;
+  double sa = 0.0, sb = 0.0;
+  for (int t = lane; t < len; t += 32) {
+    const float pa = xi[t], pb = __ldg(xj + t);
+    const float m = (pa + pb) / 2.f;
+    sa += static_cast<double>(pa * logf(pa / m));
+    sb += static_cast<double>(pb * logf(pb / m));
+  }
+  const float fa = static_cast<float>(warp_sum(sa)), fb = static_cast<float>(warp_sum(sb));
+  if (lane == 0) out[int64_t(i) * n_vec + j] = sqrtf(0.5f * fa + 0.5f * fb);
+}
+int launch_pairwise_jsd(const float* x, int n_vec, int len, float* out, cudaStream_t st) {
+  pairwise_sqrt_jsd_kernel<<<dim3(ceil_div(n_vec, 8), n_vec), 256, size_t(len) * sizeof(float), st>>>(x, n_vec, len, out);
+  return check_launch();
+}
+
 // ------------------------------------------------------------------ election / sharing
 
 // One CTA replays the reference's loop over heads in ascending order

@@ -126,6 +126,21 @@ __device__ __forceinline__ float row_max(const uint32_t (&r)[32]) {
   }
   return max3(fmaxf(a, b), __uint_as_float(r[30]), __uint_as_float(r[31]));
 }
+// maximum of a 128-element row held as four 32-register chunks: element-wise across the chunks first
+// (32 independent chains), then a 3-input tree - many short chains instead of eight long ones
+__device__ __forceinline__ float row_max4(const uint32_t (&a)[32], const uint32_t (&b)[32], const uint32_t (&c)[32],
+                                          const uint32_t (&d)[32]) {
+  float t[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    t[j] = fmaxf(max3(__uint_as_float(a[j]), __uint_as_float(b[j]), __uint_as_float(c[j])), __uint_as_float(d[j]));
+  float u[11];
+#pragma unroll
+  for (int j = 0; j < 10; ++j) u[j] = max3(t[3 * j], t[3 * j + 1], t[3 * j + 2]);
+  u[10] = fmaxf(t[30], t[31]);
+  const float v0 = max3(u[0], u[1], u[2]), v1 = max3(u[3], u[4], u[5]), v2 = max3(u[6], u[7], u[8]);
+  return max3(max3(v0, v1, v2), u[9], u[10]);
+}
 // two fp32 lanes in one 64-bit register (packed fp32x2 arithmetic of sm_100)
 __device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
   unsigned long long d;
@@ -329,6 +344,91 @@ __device__ __forceinline__ void mma_pv_group(uint32_t o_tmem, uint32_t p_tmem, u
       "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t}"
       ::"r"(o_tmem), "r"(p_tmem), "l"(v_desc), "r"(TC_IDESC_PV), "r"(acc), "n"(VSTEP) : "memory");
+}
+
+// The same products with every descriptor prepared BEFORE the first tcgen05.mma, so that the eight
+// instructions leave the issuing thread back to back.  The thread shares its scheduler with softmax
+// warps that always have something to issue: an instruction between two MMAs waits ~10-20 clk for an
+// issue slot, and the tensor pipe does not take the next MMA while it waits - four such instructions
+// per k-step made a Q K^T group take ~800 clk instead of 512.
+struct KSteps { uint64_t d[8]; };
+// K-major operand: steps 0-3 walk the first 64-element slab in 32-byte strides, 4-7 the second
+__device__ __forceinline__ void ksteps_kmajor(uint64_t base, KSteps& o) {
+  const uint32_t lo = static_cast<uint32_t>(base), hi = static_cast<uint32_t>(base >> 32);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t off = uint32_t(i >> 2) * (TC_SLAB_BYTES >> 4) + uint32_t(i & 3) * (32u >> 4);
+    o.d[i] = (uint64_t(hi) << 32) | uint64_t(lo + off);
+  }
+}
+// MN-major operand (V): 16 keys = 2048 bytes per step
+__device__ __forceinline__ void ksteps_mnmajor(uint64_t base, KSteps& o) {
+  const uint32_t lo = static_cast<uint32_t>(base), hi = static_cast<uint32_t>(base >> 32);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o.d[i] = (uint64_t(hi) << 32) | uint64_t(lo + uint32_t(i) * (2048u >> 4));
+}
+__device__ __forceinline__ void mma_qk_x8(uint32_t d_tmem, const KSteps& a, const KSteps& b) {
+  asm volatile(
+      "{\n\t.reg .pred pz, po;\n\t"
+      "setp.ne.b32 pz, 0, 0;\n\tsetp.eq.b32 po, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %10, %1, pz;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %11, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %12, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %17, %1, po;\n\t}"
+      ::"r"(d_tmem), "r"(TC_IDESC_QK),
+        "l"(a.d[0]), "l"(a.d[1]), "l"(a.d[2]), "l"(a.d[3]), "l"(a.d[4]), "l"(a.d[5]), "l"(a.d[6]), "l"(a.d[7]),
+        "l"(b.d[0]), "l"(b.d[1]), "l"(b.d[2]), "l"(b.d[3]), "l"(b.d[4]), "l"(b.d[5]), "l"(b.d[6]), "l"(b.d[7])
+      : "memory");
+}
+// O (+)= P V with P at p_tmem + 8 i (16 bf16 columns per step)
+__device__ __forceinline__ void mma_pv_x8(uint32_t o_tmem, uint32_t p_tmem, const KSteps& v, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred pa, po;\n\t"
+      "setp.ne.b32 pa, %2, 0;\n\tsetp.eq.b32 po, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %11, %1, pa;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %12, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %13, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %14, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %15, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%8], %16, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%9], %17, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%10], %18, %1, po;\n\t}"
+      ::"r"(o_tmem), "r"(TC_IDESC_PV), "r"(acc),
+        "r"(p_tmem), "r"(p_tmem + 8u), "r"(p_tmem + 16u), "r"(p_tmem + 24u), "r"(p_tmem + 32u), "r"(p_tmem + 40u),
+        "r"(p_tmem + 48u), "r"(p_tmem + 56u),
+        "l"(v.d[0]), "l"(v.d[1]), "l"(v.d[2]), "l"(v.d[3]), "l"(v.d[4]), "l"(v.d[5]), "l"(v.d[6]), "l"(v.d[7])
+      : "memory");
+}
+
+// the same product in two parts, for a P tile that becomes ready in two parts: k-steps 0-5 (the first
+// 96 keys), then k-steps 6-7
+__device__ __forceinline__ void mma_pv_first6(uint32_t o_tmem, uint32_t p_tmem, const KSteps& v, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred pa, po;\n\t"
+      "setp.ne.b32 pa, %2, 0;\n\tsetp.eq.b32 po, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %9, %1, pa;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %10, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %11, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %12, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %13, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%8], %14, %1, po;\n\t}"
+      ::"r"(o_tmem), "r"(TC_IDESC_PV), "r"(acc),
+        "r"(p_tmem), "r"(p_tmem + 8u), "r"(p_tmem + 16u), "r"(p_tmem + 24u), "r"(p_tmem + 32u), "r"(p_tmem + 40u),
+        "l"(v.d[0]), "l"(v.d[1]), "l"(v.d[2]), "l"(v.d[3]), "l"(v.d[4]), "l"(v.d[5])
+      : "memory");
+}
+__device__ __forceinline__ void mma_pv_last2(uint32_t o_tmem, uint32_t p_tmem, const KSteps& v) {
+  asm volatile(
+      "{\n\t.reg .pred po;\n\t"
+      "setp.eq.b32 po, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %4, %1, po;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %5, %1, po;\n\t}"
+      ::"r"(o_tmem), "r"(TC_IDESC_PV), "r"(p_tmem + 48u), "r"(p_tmem + 56u), "l"(v.d[6]), "l"(v.d[7])
+      : "memory");
 }
 
 // ---------------------------------------------------------------- host side

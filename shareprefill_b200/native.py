@@ -45,6 +45,7 @@ SIGNATURES = {
     "spf_sharing_state_reset": (_I, [_P, _I, _I, _P]),
     "spf_sharing_state_layout": (_I, [_I, _I, C.POINTER(C.c_int64)]),
     "spf_classify_heads": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
+    "spf_pairwise_sqrt_jsd": (_I, [_P, _I, _I, _P, _P]),
     "spf_elect_and_share": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _D, _D, _D, _I,
                                  _P, _P, _P, _P]),
     "spf_build_vs_bitmap": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
