@@ -429,6 +429,32 @@ def measure_incumbents(wl, lookup_path, cfg, peaks):
     return inc, sparse
 
 
+def bind_to_gpu_numa_node(device_index: int):
+    """Pin this process to the CPU cores of the NUMA node the GPU hangs off, so that the pinned host
+    buffers it allocates next are placed (first touch) in that node's memory: with one rank per GPU
+    all staging traffic otherwise crosses the socket interconnect of whichever node the ranks started
+    on.  Returns a short description for the JSON line; does nothing where sysfs has no answer."""
+    try:
+        pr = torch.cuda.get_device_properties(device_index)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return "no NUMA information"
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                a, _, b = part.partition("-")
+                cpus.update(range(int(a), int(b or a) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return f"node {node}: none of its cores is available to this process"
+        os.sched_setaffinity(0, cpus)
+        return f"bound to NUMA node {node} ({len(cpus)} cores)"
+    except (OSError, ValueError, AttributeError) as e:
+        return f"not bound ({type(e).__name__})"
+
+
 # ------------------------------------------------------------------------------ GPU arm
 def run_gpu_arm(args, wl):
     import torch.distributed as dist
@@ -443,6 +469,7 @@ def run_gpu_arm(args, wl):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = bind_to_gpu_numa_node(local) if world > 1 else "single process: not bound"
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     native.load()
@@ -644,7 +671,8 @@ def run_gpu_arm(args, wl):
                           "traffic": ncu_dram_bytes("pool_blocks_kernel", wl) if world == 1 else None,
                           "traffic_unit": "bytes per launch (ncu dram read+write)", "of": peaks["source"]},
         "cpu_baseline": cpu,
-        "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
+        "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                "host_buffers": numa},
         "gpu_launches": launches_timed,
         "device_timeouts": timeouts,
         "clocks": clocks,

@@ -100,7 +100,9 @@ int spf_lastblock_profile(const void* q, int64_t q_stride_n, int64_t q_stride_h,
  *     covers n_q_heads * (ceil(n_tokens/128) + 1) <= 8320, e.g. 32 heads x 32K tokens or
  *     8 heads x 128K tokens.
  *   - The first call on a device looks up the array's device address (that device must be
- *     current); make that first call outside any stream capture.
+ *     current); make that first call outside any stream capture.  The address is kept for the
+ *     life of the process and is only valid while that device's context lives: do not call this
+ *     function again after cudaDeviceReset() (or after the primary context was released).
  *   - The function calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - All calls on a device share the one array: calls that may overlap on the GPU (different
  *     streams, threads or processes sharing a context) race; serialise them.  Nothing in the

@@ -68,21 +68,20 @@ def shareprefill_attention_core(module, query_states, key_states, value_states, 
         return out[None], attn_weights
 
     # decode step (one query token): dense attention over the cache with the split-K decode kernel;
-    # the reference calls flash_attn_func here (attn/shareprefill_attn.py:146-153)
-    if (query_states.is_cuda and query_states.dtype == torch.bfloat16 and not module.training
+    # the reference calls flash_attn_func here (attn/shareprefill_attn.py:146-153), which takes bf16 /
+    # fp16 only and applies attention dropout in training mode.  This path has one kernel and no
+    # library fallback: dropout (training with attention_dropout > 0) and other dtypes are refused.
+    dropout = float(getattr(module, "attention_dropout", 0.0) or 0.0) if module.training else 0.0
+    if (query_states.is_cuda and query_states.dtype == torch.bfloat16 and dropout == 0.0
             and head_dim in (64, 128)):
         outs = []
         for b in range(bsz):
             outs.append(native.decode_attention(query_states[b, :, 0, :], _token_major(key_states[b]),
                                                 _token_major(value_states[b]), softmax_scale))
         return torch.stack(outs)[:, None], None
-    # anything else (training-time dropout, other dtypes): torch's dense attention
-    groups = num_heads // key_states.shape[1]
-    out = torch.nn.functional.scaled_dot_product_attention(
-        query_states, key_states, value_states,
-        dropout_p=module.attention_dropout if module.training else 0.0,
-        scale=softmax_scale, is_causal=False, enable_gqa=groups > 1)
-    return out.transpose(1, 2).contiguous(), None
+    raise native.SpfError(
+        "decode step: the B200 kernel needs CUDA bfloat16 tensors, head_dim 64 or 128 and no attention "
+        f"dropout (got {query_states.dtype} on {query_states.device}, head_dim {head_dim}, dropout {dropout})")
 
 
 def dense_avg_attn(sharing, pat, num_heads: int) -> torch.Tensor:

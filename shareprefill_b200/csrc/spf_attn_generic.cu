@@ -149,16 +149,19 @@ __global__ void __launch_bounds__(BS * 2) sparse_attn_generic_kernel(const AttnP
     }
   };
 
+  // the pivot-only pass needs the row statistics (running maximum and sum) of this sweep, not its
+  // output: V is not loaded and P V is not computed there
+  const bool with_v = !p.pivot_only;
   RowWalker walk;
   walk.init(brow, r);
   int col = walk.next();
   int stage = 0;
-  if (col >= 0) issue_kv(col, 0, true);
+  if (col >= 0) issue_kv(col, 0, with_v);
   cp_async_commit();
 
   while (col >= 0) {
     const int nxt = walk.next();
-    if (nxt >= 0) issue_kv(nxt, stage ^ 1, true);
+    if (nxt >= 0) issue_kv(nxt, stage ^ 1, with_v);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -202,22 +205,24 @@ __global__ void __launch_bounds__(BS * 2) sparse_attn_generic_kernel(const AttnP
       rs[i] += __shfl_xor_sync(0xffffffffu, rs[i], 2);
       l_run[i] = l_run[i] * alpha[i] + rs[i];
     }
+    if (with_v) {
 #pragma unroll
-    for (int i = 0; i < NTILES_O; ++i) {
-      o_acc[i][0] *= alpha[0]; o_acc[i][1] *= alpha[0];
-      o_acc[i][2] *= alpha[1]; o_acc[i][3] *= alpha[1];
-    }
-    // O += P V
-    const uint32_t vb = sbase + (stage * 2 + 1) * TILE_BYTES;
+      for (int i = 0; i < NTILES_O; ++i) {
+        o_acc[i][0] *= alpha[0]; o_acc[i][1] *= alpha[0];
+        o_acc[i][2] *= alpha[1]; o_acc[i][3] *= alpha[1];
+      }
+      // O += P V
+      const uint32_t vb = sbase + (stage * 2 + 1) * TILE_BYTES;
 #pragma unroll
-    for (int kk = 0; kk < BS / 16; ++kk) {
+      for (int kk = 0; kk < BS / 16; ++kk) {
 #pragma unroll
-      for (int ip = 0; ip < NTILES_O / 2; ++ip) {
-        uint32_t bf[4];
-        const int vrow = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        ldmatrix_x4_trans(bf, vb + tile_off<D>(vrow, ip * 2 + (lane >> 4)));
-        mma_bf16_16816(o_acc[2 * ip], pf[kk], bf[0], bf[1]);
-        mma_bf16_16816(o_acc[2 * ip + 1], pf[kk], bf[2], bf[3]);
+        for (int ip = 0; ip < NTILES_O / 2; ++ip) {
+          uint32_t bf[4];
+          const int vrow = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          ldmatrix_x4_trans(bf, vb + tile_off<D>(vrow, ip * 2 + (lane >> 4)));
+          mma_bf16_16816(o_acc[2 * ip], pf[kk], bf[0], bf[1]);
+          mma_bf16_16816(o_acc[2 * ip + 1], pf[kk], bf[2], bf[3]);
+        }
       }
     }
     __syncthreads();  // everyone is done with `stage` before it is refilled

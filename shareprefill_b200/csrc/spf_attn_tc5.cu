@@ -30,17 +30,20 @@
 namespace spf {
 
 constexpr int TC_THREADS = 384;                             // 3 warpgroups: control, softmax A, softmax B
-constexpr int TC_REGS_CONTROL = 128, TC_REGS_SOFTMAX = 184; // setmaxnreg targets
+#ifndef TC5_REGS_CONTROL
+#define TC5_REGS_CONTROL 128
+#define TC5_REGS_SOFTMAX 184
+#endif
+constexpr int TC_REGS_CONTROL = TC5_REGS_CONTROL, TC_REGS_SOFTMAX = TC5_REGS_SOFTMAX; // setmaxnreg targets
 static_assert(4 * TC_REGS_CONTROL + 8 * TC_REGS_SOFTMAX <= 12 * 168, "setmaxnreg targets exceed the CTA's register pool");
 constexpr int TC_KSTAGES = 3;
 constexpr int TC_VSTAGES = 2;
-// shared memory map: 3 KiB of control data, then 1024-byte aligned tiles (Q x2, K x3, V x2)
+// shared memory map: 1 KiB of control data, then 1024-byte aligned tiles (Q x2, K x3, V x2)
 constexpr uint32_t TC_SMEM_CTRL = 0;                        // mbarriers, TMEM slot, abort flag
-constexpr uint32_t TC_SMEM_XCH = 1024;                      // [2 heads][128 rows][2] half-row sums of the two threads of a row
-constexpr uint32_t TC_SMEM_Q = 3072;
+constexpr uint32_t TC_SMEM_Q = 1024;
 constexpr uint32_t TC_SMEM_K = TC_SMEM_Q + 2 * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_V = TC_SMEM_K + TC_KSTAGES * TC_TILE_BYTES;
-constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_V + TC_VSTAGES * TC_TILE_BYTES;   // 232448 bytes: the 227 KiB limit
+constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_V + TC_VSTAGES * TC_TILE_BYTES;   // 225 KiB of the 227 KiB limit
 constexpr float TC_RESCALE_LOG2 = 8.0f;
 // of every 8 element pairs of a score row, this many get their exponential from the FMA-pipe polynomial
 #ifndef TC5_POLY_PAIRS
@@ -59,17 +62,16 @@ constexpr float TC_RESCALE_LOG2 = 8.0f;
 #ifndef TC5_SPLIT_P
 #define TC5_SPLIT_P 0
 #endif
-// 1: all eight softmax warps work on ONE head's score tile at a time, two threads per query row (64 key
-// columns each), head A's tile then head B's: a softmax step takes half as long, which shortens the
-// chain softmax -> P V -> Q K^T -> softmax of a head, and the MMAs of one head run under the softmax of
-// the other.  0: a warpgroup per head, a thread per row.
-#ifndef TC5_PAIR_ROWS
-#define TC5_PAIR_ROWS 0
+// 1: the sixteen MMAs of a head's step leave the issuing thread back to back from descriptors prepared
+// beforehand; 0: the descriptor of each k-step is derived from the previous one between two MMAs
+#ifndef TC5_B2B
+#define TC5_B2B 1
 #endif
-#if TC5_PAIR_ROWS && TC5_SPLIT_P
-#error "TC5_SPLIT_P is not implemented for TC5_PAIR_ROWS"
+// 1: every head of a pair always has its own issuing thread (warps 1 and 2)
+#ifndef TC5_ALWAYS_SPLIT
+#define TC5_ALWAYS_SPLIT 0
 #endif
-constexpr uint32_t TC_P_ARRIVALS = (TC5_WARP_ARRIVE ? 4u : 128u) * (TC5_PAIR_ROWS ? 2u : 1u);
+constexpr uint32_t TC_P_ARRIVALS = TC5_WARP_ARRIVE ? 4u : 128u;
 
 // Timing probe, compiled in only with -DSPF_TC5_TRACE: clock64() stamps of the first CTA's
 // first 64 iterations, [role: softmax A, softmax B, MMA issuer][iteration][slot].
@@ -141,6 +143,13 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   auto bar_pearly = [&](int h) { return bar0 + 8u * (17 + h); };   // first three quarters of P written
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_SMEM_CTRL + 8 * 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_SMEM_CTRL + 8 * 19 + 8);
+  // shared-memory descriptors of all k-steps of every operand tile, written once: Q of head A and B
+  // (2 x 8), the K stages (3 x 8), the V stages (2 x 8).  The issuing threads fetch the eight
+  // descriptors of a tile with four 16-byte loads instead of deriving them (their instruction stream
+  // competes with the softmax warps for issue slots).
+  uint64_t* dtab = reinterpret_cast<uint64_t*>(smem + TC_SMEM_CTRL + 256);
+  constexpr int DT_Q = 0, DT_K = 16, DT_V = 16 + 8 * TC_KSTAGES, DT_N = DT_V + 8 * TC_VSTAGES;
+  static_assert(256 + DT_N * 8 <= TC_SMEM_Q, "descriptor table does not fit the control region");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // CTAs that run at the same time belong to the same KV head (its K/V stream stays in L2);
@@ -166,6 +175,20 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     *abort_flag = 0;
     fence_barrier_init();
+  }
+  if (tid >= 64 && tid < 64 + DT_N) {
+    const int e = tid - 64, ks = e & 7;
+    uint64_t d;
+    if (e < DT_K) {
+      d = desc_kmajor(sbase + TC_SMEM_Q + uint32_t(e >> 3) * TC_TILE_BYTES) +
+          uint64_t(uint32_t(ks >> 2) * (TC_SLAB_BYTES >> 4) + uint32_t(ks & 3) * (32u >> 4));
+    } else if (e < DT_V) {
+      d = desc_kmajor(sbase + TC_SMEM_K + uint32_t((e - DT_K) >> 3) * TC_TILE_BYTES) +
+          uint64_t(uint32_t(ks >> 2) * (TC_SLAB_BYTES >> 4) + uint32_t(ks & 3) * (32u >> 4));
+    } else {
+      d = desc_mnmajor(sbase + TC_SMEM_V + uint32_t((e - DT_V) >> 3) * TC_TILE_BYTES) + uint64_t(uint32_t(ks) * (2048u >> 4));
+    }
+    dtab[e] = d;
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512u));
@@ -257,7 +280,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     cnt_u = __reduce_add_sync(0xffffffffu, cnt_u);
     if (lane == 0) {
       const int me = warp - 1;
-      const bool split = hasB && 4 * cnt_u > 5 * max(cnt_a, cnt_b);
+      const bool split = hasB && (TC5_ALWAYS_SPLIT || 4 * cnt_u > 5 * max(cnt_a, cnt_b));
       // descriptors differ from a base only in the 14-bit address field: one 64-bit add per operand
       const uint64_t qdA = desc_kmajor(sbase + TC_SMEM_Q), qdB = desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES);
       const uint64_t kd0 = desc_kmajor(sbase + TC_SMEM_K), vd0 = desc_mnmajor(sbase + TC_SMEM_V);
@@ -266,15 +289,27 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // checked, the descriptors of all sixteen k-steps built - so that after the wait for P the
       // instructions between the fence and the last MMA are MMAs only.
       auto head_step = [&](int h, bool do_pv, bool do_qk, int vs_stage, int ks_stage, bool accumulate) {
+#if TC5_B2B
         KSteps vd, qd, kd;
-        if (do_pv) ksteps_mnmajor(vd0 + uint64_t((vs_stage * TC_TILE_BYTES) >> 4), vd);
-        if (do_qk) {
-          ksteps_kmajor(h == 0 ? qdA : qdB, qd);
-          ksteps_kmajor(kd0 + uint64_t((ks_stage * TC_TILE_BYTES) >> 4), kd);
-        }
+        auto fetch = [&](int first, KSteps& o) {
+          const ulonglong2* src = reinterpret_cast<const ulonglong2*>(dtab + first);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const ulonglong2 t = src[j]; o.d[2 * j] = t.x; o.d[2 * j + 1] = t.y; }
+        };
+        if (do_pv) fetch(DT_V + 8 * vs_stage, vd);
+        if (do_qk) { fetch(DT_Q + 8 * h, qd); fetch(DT_K + 8 * ks_stage, kd); }
+#else
+        const uint64_t vd = vd0 + uint64_t((vs_stage * TC_TILE_BYTES) >> 4), qd = h == 0 ? qdA : qdB,
+                       kd = kd0 + uint64_t((ks_stage * TC_TILE_BYTES) >> 4);
+#endif
         const uint32_t ts = tmem + (h == 0 ? 0u : 128u), to = tmem + (h == 0 ? 256u : 384u);
         // phase 0 (TC5_SPLIT_P only): the first six k-steps of P V; phase 1: the rest
         return [=](int phase) {
+#if !TC5_B2B
+          (void)phase;
+          if (do_pv) mma_pv_group(to, ts, vd, accumulate ? 1u : 0u);
+          if (do_qk) { mma_qk_group(ts, qd, kd); tc_commit(bar_sfull(h)); }
+#else
 #if TC5_SPLIT_P
           if (phase == 0) { if (do_pv) mma_pv_first6(to, ts, vd, accumulate ? 1u : 0u); return; }
           if (do_pv) mma_pv_last2(to, ts, vd);
@@ -282,6 +317,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (do_pv) mma_pv_x8(to, ts, vd, accumulate ? 1u : 0u);
 #endif
           if (do_qk) { mma_qk_x8(ts, qd, kd); tc_commit(bar_sfull(h)); }
+#endif
         };
       };
       bool ok = mbar_wait(bar_q, 0, abort_flag);
@@ -387,137 +423,6 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   } else {
     // ------------------------------------------------------------ softmax warpgroups
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TC_REGS_SOFTMAX));
-#if TC5_PAIR_ROWS
-    // ---- two threads per query row: warp 4+q and warp 8+q share the rows of TMEM lane quarter q (and
-    // scheduler q).  Both read the whole score row for its maximum - so they reach the same decisions
-    // without talking to each other - and `half` picks the 64 key columns whose exponentials, and the
-    // 64 output columns whose final scaling, this thread does.  The only value passed between the two
-    // is the half-row sum, left in shared memory before every hand-over of P and read once at the end.
-    const int half = (warp - 4) >> 2;
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    float* xch = reinterpret_cast<float*>(smem + TC_SMEM_XCH);     // [2 heads][128 rows][2 halves]
-    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;  // reference point and half-row sum per head
-    int k_a = 0, k_b = 0;
-    bool ok = true;
-    {
-      PairWalker wk; wk.init(rowA, rowB, r);
-      int fl;
-      for (int col = wk.next(fl); col >= 0 && ok; col = wk.next(fl)) {
-        const bool diag = (col == r);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (!(fl & (1 << h)) || !ok) continue;
-          const int k = h == 0 ? k_a : k_b;
-          float m_used = h == 0 ? m_a : m_b;
-          float l_sum = h == 0 ? l_a : l_b;
-          const uint32_t tS = tmem + lane_base + uint32_t(h * 128);
-          const uint32_t tP = tmem + lane_base + uint32_t(h * 128 + half * 32);
-          const uint32_t tO = tmem + lane_base + uint32_t(256 + h * 128 + half * 64);
-          const bool tracer = lane == 0 && quarter == 0 && half == 0;
-          if (tracer) TRACE(h, k, 0);
-          ok = mbar_wait(bar_sfull(h), k & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          if (tracer) TRACE(h, k, 1);
-          // own half (kept for the exponentials) and the other half (only its maximum is needed)
-          uint32_t s0[32], s1[32], t0[32], t1[32];
-          tmem_ld32_raw(tS + uint32_t(half * 64), s0);
-          tmem_ld32_raw(tS + uint32_t(half * 64 + 32), s1);
-          tmem_ld32_raw(tS + uint32_t((half ^ 1) * 64), t0);
-          tmem_ld32_raw(tS + uint32_t((half ^ 1) * 64 + 32), t1);
-          tc_wait_ld();
-          if (tracer) TRACE(h, k, 2);
-          if (diag) {
-            mask_after(s0, row - half * 64);
-            mask_after(s1, row - half * 64 - 32);
-            mask_after(t0, row - (half ^ 1) * 64);
-            mask_after(t1, row - (half ^ 1) * 64 - 32);
-          }
-          const float mb = row_max4(s0, s1, t0, t1) * p.scale_log2;
-          if (tracer) TRACE(h, k, 5);
-          float alpha = 1.f;
-          bool grow = false;
-          if (k == 0) {
-            m_used = mb;
-          } else if (mb > m_used + TC_RESCALE_LOG2) {
-            alpha = exp2f(m_used - mb);
-            m_used = mb;
-            l_sum *= alpha;
-            grow = true;
-          }
-          if (__any_sync(0xffffffffu, grow)) {
-            // S_h(k) is complete, hence so is every earlier P V of this head: O_h is stable
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-              float v[32];
-              tmem_ld32(tO + c * 32, v);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] *= alpha;
-              tmem_st32(tO + c * 32, v);
-            }
-          }
-          float l0 = 0.f, l1 = 0.f;
-          uint32_t pk[16];
-          exp_pack_mixed<TC5_POLY_PAIRS>(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tP + 0, pk);
-          exp_pack_mixed<TC5_POLY_PAIRS>(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tP + 16, pk);
-          l_sum += l0 + l1;
-          xch[(h * 128 + row) * 2 + half] = l_sum;
-          if (tracer) TRACE(h, k, 3);
-          tc_wait_st();
-          if (tracer) TRACE(h, k, 6);
-          tc_fence_before();
-#if TC5_WARP_ARRIVE
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_pready(h));
-#else
-          mbar_arrive(bar_pready(h));
-#endif
-          if (tracer) TRACE(h, k, 4);
-          if (h == 0) { k_a = k + 1; m_a = m_used; l_a = l_sum; } else { k_b = k + 1; m_b = m_used; l_b = l_sum; }
-        }
-      }
-      // ---- epilogue: this thread writes 64 of the row's 128 output columns, per head
-      const int tok = row0 + row;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int head = h == 0 ? hA : hB;
-        if (head < 0 || !ok) continue;
-        const int k = h == 0 ? k_a : k_b;
-        const uint32_t tO = tmem + lane_base + uint32_t(256 + h * 128 + half * 64);
-        __nv_bfloat16* orow = p.out + (int64_t(tok) * p.n_q_heads + head) * TC_D + half * 64;
-        if (k > 0) ok = mbar_wait(bar_odone(h), 0, abort_flag);
-        if (!ok) continue;
-        tc_fence_after();
-        // the other half's sum was stored before that thread's last hand-over of P, which the last
-        // P V - and so this barrier - came after
-        const float l_row = k > 0 ? (h == 0 ? l_a : l_b) + xch[(h * 128 + row) * 2 + (half ^ 1)] : 0.f;
-        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          float v[32];
-          if (k > 0) {
-            tmem_ld32(tO + c * 32, v);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0.f;
-          }
-          if (tok < p.n_tokens) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o;
-              o.x = pack2_bf16(v[j] * inv, v[j + 1] * inv);
-              o.y = pack2_bf16(v[j + 2] * inv, v[j + 3] * inv);
-              o.z = pack2_bf16(v[j + 4] * inv, v[j + 5] * inv);
-              o.w = pack2_bf16(v[j + 6] * inv, v[j + 7] * inv);
-              *reinterpret_cast<uint4*>(orow + c * 32 + j) = o;
-            }
-          }
-        }
-      }
-    }
-#else
     const int h = (warp - 4) >> 2;                 // 0: head A, 1: head B
     const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;           // query row within the block
@@ -640,7 +545,6 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
     }
-#endif  // TC5_PAIR_ROWS
   }
   __syncwarp();
   tc_fence_before();

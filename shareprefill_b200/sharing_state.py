@@ -74,6 +74,7 @@ class AttentionSharing:
         self._slot_tables: Dict[Tuple[int, int, str], torch.Tensor] = {}
         self._layer_shares: Dict[Tuple[int, int], bool] = {}
         self._state: Optional[native.SharingStateBuffer] = None
+        self._qa_scores: Optional[torch.Tensor] = None
         self._needs_reset = True
         self.last_pattern: Optional[BlockPattern] = None
         self.on_stage = None   # optional callable(stage_name), e.g. to record CUDA events
@@ -162,9 +163,23 @@ class AttentionSharing:
         """
         ctx = self.profile_heads(q, k, layer_idx, num_heads, block_size, min_budget, max_budget,
                                  pattern_threshold, gqa_interleave, stage_inputs)
-        jsd_qa_all = ctx["jsd_qa"] if self.exchange is None else self.exchange.gather_heads(ctx["jsd_qa"])
-        return self.select_blocks(ctx, jsd_qa_all, similarity_threshold, fallback_threshold,
-                                  queryaware_threshold)
+        return self.select_blocks(ctx, self._all_heads_divergence(ctx), similarity_threshold,
+                                  fallback_threshold, queryaware_threshold)
+
+    def _all_heads_divergence(self, ctx: dict) -> torch.Tensor:
+        """Every head's query-aware divergence, as the election needs it.  With the heads sharded, the
+        other ranks' values come through the exchange - but only in layers where some head belongs
+        to a shared cluster: elsewhere no pivot can be elected, a head's flags depend on its own
+        divergence alone, and the collective (a synchronisation point of all ranks) is skipped; the
+        entries of the other ranks' heads are then NaN, which the election reads as "nothing to do"."""
+        local = ctx["jsd_qa"]
+        if self.exchange is None:
+            return local
+        if self.layer_can_share(ctx["layer"], ctx["num_heads"]):
+            return self.exchange.gather_heads(local)
+        full = torch.full((ctx["num_heads"],), float("nan"), dtype=local.dtype, device=local.device)
+        full[ctx["h0"]:ctx["h0"] + local.numel()] = local
+        return full
 
     def profile_heads(self, q, k, layer_idx, num_heads, block_size, min_budget, max_budget,
                       pattern_threshold=0.9, gqa_interleave=False, stage_inputs=None) -> dict:
@@ -216,7 +231,14 @@ class AttentionSharing:
         bitmap = native.build_vs_bitmap(vpool, spool, nv, ns, flags, ctx["slot_local"], state)
         scores = ctx["qa_scores"]
         if scores is None:
-            scores = native.query_aware_scores(ctx["avg_q"], ctx["avg_k"], flags)
+            # one buffer per shape, reused by every layer and never cleared: only the rows of query-aware
+            # heads are written (in full) and read
+            nb_, h_ = ctx["nb"], ctx["avg_q"].shape[1]
+            buf = self._qa_scores
+            if buf is None or buf.shape != (h_, nb_, nb_) or buf.device != ctx["avg_q"].device:
+                buf = torch.empty(h_, nb_, nb_, dtype=torch.float32, device=ctx["avg_q"].device)
+                self._qa_scores = buf
+            scores = native.query_aware_scores(ctx["avg_q"], ctx["avg_k"], flags, scores=buf)
         native.query_aware_select(scores, flags, ctx["pattern_threshold"], bitmap)
         pat = BlockPattern(bitmap, flags, ctx["slot_local"], ctx["nb"], nv, ns,
                            info={"can_share": self.layer_can_share(ctx["layer"], ctx["num_heads"]),
