@@ -31,8 +31,8 @@ namespace spf {
 
 constexpr int TC_THREADS = 384;                             // 3 warpgroups: control, softmax A, softmax B
 #ifndef TC5_REGS_CONTROL
-#define TC5_REGS_CONTROL 128
-#define TC5_REGS_SOFTMAX 184
+#define TC5_REGS_CONTROL 88
+#define TC5_REGS_SOFTMAX 208
 #endif
 constexpr int TC_REGS_CONTROL = TC5_REGS_CONTROL, TC_REGS_SOFTMAX = TC5_REGS_SOFTMAX; // setmaxnreg targets
 static_assert(4 * TC_REGS_CONTROL + 8 * TC_REGS_SOFTMAX <= 12 * 168, "setmaxnreg targets exceed the CTA's register pool");
@@ -65,11 +65,15 @@ constexpr float TC_RESCALE_LOG2 = 8.0f;
 // 1: the sixteen MMAs of a head's step leave the issuing thread back to back from descriptors prepared
 // beforehand; 0: the descriptor of each k-step is derived from the previous one between two MMAs
 #ifndef TC5_B2B
-#define TC5_B2B 1
+#define TC5_B2B 0
 #endif
 // 1: every head of a pair always has its own issuing thread (warps 1 and 2)
 #ifndef TC5_ALWAYS_SPLIT
 #define TC5_ALWAYS_SPLIT 0
+#endif
+// rows in which neither head visits more than this many blocks also get an issuing thread per head
+#ifndef TC5_SPLIT_SHORT
+#define TC5_SPLIT_SHORT 0
 #endif
 constexpr uint32_t TC_P_ARRIVALS = TC5_WARP_ARRIVE ? 4u : 128u;
 
@@ -201,8 +205,8 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   if (warp < 4) {
     // control warpgroup (producer, MMA issuers, an idle warp) hands registers to the softmax warpgroups.
-    // The CTA owns the registers it was launched with (384 threads x 168) and no more: 4 warps x 128 +
-    // 8 warps x 184 stays within that pool; a sum beyond it would leave the last setmaxnreg.inc waiting
+    // The CTA owns the registers it was launched with (384 threads x 168) and no more: 4 warps x 88 +
+    // 8 warps x 208 stays within that pool; a sum beyond it would leave the last setmaxnreg.inc waiting
     // for ever.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_REGS_CONTROL));
   if (warp == 0) {
@@ -280,7 +284,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     cnt_u = __reduce_add_sync(0xffffffffu, cnt_u);
     if (lane == 0) {
       const int me = warp - 1;
-      const bool split = hasB && (TC5_ALWAYS_SPLIT || 4 * cnt_u > 5 * max(cnt_a, cnt_b));
+      const bool split = hasB && (TC5_ALWAYS_SPLIT || 4 * cnt_u > 5 * max(cnt_a, cnt_b) || max(cnt_a, cnt_b) <= TC5_SPLIT_SHORT);
       // descriptors differ from a base only in the 14-bit address field: one 64-bit add per operand
       const uint64_t qdA = desc_kmajor(sbase + TC_SMEM_Q), qdB = desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES);
       const uint64_t kd0 = desc_kmajor(sbase + TC_SMEM_K), vd0 = desc_mnmajor(sbase + TC_SMEM_V);
