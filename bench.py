@@ -338,7 +338,8 @@ def _event_ms(fn, warmup=1, reps=3):
 
 
 def one_layer_ours(wl, q, k, v, lookup_path, cfg, reps=3):
-    """One layer of this path on resident inputs: (ms, per-stage ms, visited blocks, visited fraction)."""
+    """One layer of this path on resident inputs: (ms, per-stage ms, visited blocks weighted by their
+    flops - a pivot's block counts 1.5 -, visited fraction)."""
     from shareprefill_b200 import native
     from shareprefill_b200.attention import sparse_prefill_attention
     from shareprefill_b200.sharing_state import AttentionSharing
@@ -357,9 +358,12 @@ def one_layer_ours(wl, q, k, v, lookup_path, cfg, reps=3):
     torch.cuda.synchronize()
     sharing.on_stage = None
     stage = {n1: e0.elapsed_time(e1) for (_, e0), (n1, e1) in zip(marks[:-1], marks[1:])}
-    blocks = int(native.bitmap_row_counts(pat.bitmap)[1].sum())
+    tot = native.bitmap_row_counts(pat.bitmap)[1]
+    blocks = int(tot.sum())
+    # heads elected pivot in this layer also get the block-mass sweep: half the flops of a visit again
+    pivot_blocks = int(tot[(pat.flags & native.HEAD_PIVOT) != 0].sum())
     tri = wl.num_blocks * (wl.num_blocks + 1) // 2
-    return ms, stage, blocks, blocks / (tri * wl.num_q_heads)
+    return ms, stage, blocks + 0.5 * pivot_blocks, blocks / (tri * wl.num_q_heads)
 
 
 def _recorded_event():

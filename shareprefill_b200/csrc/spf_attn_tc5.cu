@@ -7,13 +7,16 @@
 //   warp 0      TMA producer: Q tiles once, then K and V tiles of the union of both heads' bitmap
 //               rows through a 3-deep K ring and a 2-deep V ring (cp.async.bulk.tensor, 128-byte
 //               swizzle, no multicast)
-//   warps 1, 2  MMA issuers: S_h = Q_h K^T (both operands in shared memory) and O_h += P_h V (P_h read
-//               from TMEM, V from shared memory) with tcgen05.mma, accumulators in TMEM; completion is
-//               signalled to mbarriers with tcgen05.commit.  Warp 1 alone alternates between the
-//               heads where they visit the same blocks; where their lists differ each head gets its
-//               own issuer, so neither waits for the other's softmax
-//   warp 3      idle (it only completes the control warpgroup, which gives most of its registers
-//               to the softmax warpgroups with setmaxnreg)
+//   warps 1, 2  MMA issuers, one per head: S_h = Q_h K^T (both operands in shared memory) and
+//               O_h += P_h V (P_h read from TMEM, V from shared memory) with tcgen05.mma, accumulators
+//               in TMEM; completion is signalled to mbarriers with tcgen05.commit.  The sixteen MMAs of
+//               a step (P V of the current block, Q K^T of the next) leave the thread back to back,
+//               their descriptors fetched from a table in shared memory.  Where the two heads visit
+//               (nearly) the same blocks a token passed between the two threads keeps the steps in the
+//               order A, B, A, B, which holds the two softmax warpgroups half a period apart; where the
+//               lists differ the threads run free, so neither head waits for the other's softmax
+//   warp 3      idle (it only completes the control warpgroup, which gives registers to the softmax
+//               warpgroups with setmaxnreg)
 //   warps 4-7   softmax warpgroup of head A: a thread owns one query row; tcgen05.ld of S, base-2
 //               online softmax with scale*log2(e) folded in, P rounded to bf16 and written back
 //               over S with tcgen05.st, O rescaled in TMEM only when the running maximum moved by
@@ -30,55 +33,26 @@
 namespace spf {
 
 constexpr int TC_THREADS = 384;                             // 3 warpgroups: control, softmax A, softmax B
-#ifndef TC5_REGS_CONTROL
-#define TC5_REGS_CONTROL 88
-#define TC5_REGS_SOFTMAX 208
-#endif
-constexpr int TC_REGS_CONTROL = TC5_REGS_CONTROL, TC_REGS_SOFTMAX = TC5_REGS_SOFTMAX; // setmaxnreg targets
+// setmaxnreg targets.  The CTA owns the registers it was launched with (384 threads x 168) and no more:
+// a sum beyond that pool would leave the last setmaxnreg.inc waiting for ever.
+constexpr int TC_REGS_CONTROL = 128, TC_REGS_SOFTMAX = 184;
 static_assert(4 * TC_REGS_CONTROL + 8 * TC_REGS_SOFTMAX <= 12 * 168, "setmaxnreg targets exceed the CTA's register pool");
 constexpr int TC_KSTAGES = 3;
 constexpr int TC_VSTAGES = 2;
 // shared memory map: 1 KiB of control data, then 1024-byte aligned tiles (Q x2, K x3, V x2)
-constexpr uint32_t TC_SMEM_CTRL = 0;                        // mbarriers, TMEM slot, abort flag
+constexpr uint32_t TC_SMEM_CTRL = 0;                        // mbarriers, TMEM slot, abort flag, descriptor table
+constexpr uint32_t TC_SMEM_DTAB = 256;
 constexpr uint32_t TC_SMEM_Q = 1024;
 constexpr uint32_t TC_SMEM_K = TC_SMEM_Q + 2 * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_V = TC_SMEM_K + TC_KSTAGES * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_V + TC_VSTAGES * TC_TILE_BYTES;   // 225 KiB of the 227 KiB limit
 constexpr float TC_RESCALE_LOG2 = 8.0f;
-// of every 8 element pairs of a score row, this many get their exponential from the FMA-pipe polynomial
-#ifndef TC5_POLY_PAIRS
-#define TC5_POLY_PAIRS 0
-#endif
-// 1: one elected lane per softmax warp arrives on the "P ready" barrier (4 arrivals) instead of every thread (128)
-#ifndef TC5_WARP_ARRIVE
-#define TC5_WARP_ARRIVE 0
-#endif
-// 1: the row maximum is reduced element-wise across the four chunks first (short dependency chains)
-#ifndef TC5_MAX_TREE
-#define TC5_MAX_TREE 0
-#endif
-// 1: P is handed over in two parts (keys 0-95 as soon as they are written, then keys 96-127), so that
-// the first six k-steps of P V run under the last quarter of the exponentials
-#ifndef TC5_SPLIT_P
-#define TC5_SPLIT_P 0
-#endif
-// 1: the sixteen MMAs of a head's step leave the issuing thread back to back from descriptors prepared
-// beforehand; 0: the descriptor of each k-step is derived from the previous one between two MMAs
-#ifndef TC5_B2B
-#define TC5_B2B 0
-#endif
-// 1: every head of a pair always has its own issuing thread (warps 1 and 2)
-#ifndef TC5_ALWAYS_SPLIT
-#define TC5_ALWAYS_SPLIT 0
-#endif
-// rows in which neither head visits more than this many blocks also get an issuing thread per head
-#ifndef TC5_SPLIT_SHORT
-#define TC5_SPLIT_SHORT 0
-#endif
-constexpr uint32_t TC_P_ARRIVALS = TC5_WARP_ARRIVE ? 4u : 128u;
+// descriptor table: the eight k-step descriptors of Q_A, Q_B, every K stage and every V stage
+constexpr int DT_Q = 0, DT_K = 16, DT_V = DT_K + 8 * TC_KSTAGES, DT_N = DT_V + 8 * TC_VSTAGES;
+static_assert(TC_SMEM_DTAB + DT_N * 8 <= TC_SMEM_Q, "descriptor table does not fit the control region");
 
 // Timing probe, compiled in only with -DSPF_TC5_TRACE: clock64() stamps of the first CTA's
-// first 64 iterations, [role: softmax A, softmax B, MMA issuer][iteration][slot].
+// first 64 iterations, [role: softmax A, softmax B, MMA issuer A][iteration][slot].
 #ifdef SPF_TC5_TRACE
 __device__ long long g_tc5_trace[3][64][8];
 #define TRACE(role, it, slot) do { if (blockIdx.x == 0 && (it) < 64) g_tc5_trace[role][it][slot] = clock64(); } while (0)
@@ -144,16 +118,15 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   auto bar_sfull = [&](int h) { return bar0 + 8u * (11 + h); };
   auto bar_pready = [&](int h) { return bar0 + 8u * (13 + h); };
   auto bar_odone = [&](int h) { return bar0 + 8u * (15 + h); };
-  auto bar_pearly = [&](int h) { return bar0 + 8u * (17 + h); };   // first three quarters of P written
+  auto bar_token = [&](int h) { return bar0 + 8u * (17 + h); };    // issuing thread h may issue its next step
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + TC_SMEM_CTRL + 8 * 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + TC_SMEM_CTRL + 8 * 19 + 8);
-  // shared-memory descriptors of all k-steps of every operand tile, written once: Q of head A and B
-  // (2 x 8), the K stages (3 x 8), the V stages (2 x 8).  The issuing threads fetch the eight
-  // descriptors of a tile with four 16-byte loads instead of deriving them (their instruction stream
-  // competes with the softmax warps for issue slots).
-  uint64_t* dtab = reinterpret_cast<uint64_t*>(smem + TC_SMEM_CTRL + 256);
-  constexpr int DT_Q = 0, DT_K = 16, DT_V = 16 + 8 * TC_KSTAGES, DT_N = DT_V + 8 * TC_VSTAGES;
-  static_assert(256 + DT_N * 8 <= TC_SMEM_Q, "descriptor table does not fit the control region");
+  // Shared-memory descriptors of all k-steps of every operand tile, written once.  An issuing thread
+  // fetches the eight descriptors of a tile with four 16-byte loads instead of deriving them: its
+  // instruction stream shares a scheduler with softmax warps that always have something to issue, and
+  // an instruction between two MMAs keeps the tensor pipe waiting (four per k-step made a Q K^T group
+  // take ~800 clk instead of 512).
+  uint64_t* dtab = reinterpret_cast<uint64_t*>(smem + TC_SMEM_DTAB);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // CTAs that run at the same time belong to the same KV head (its K/V stream stays in L2);
@@ -174,24 +147,20 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int s = 0; s < TC_KSTAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_kempty(s), 2); }
     for (int s = 0; s < TC_VSTAGES; ++s) { mbar_init(bar_vfull(s), 1); mbar_init(bar_vempty(s), 2); }
     for (int h = 0; h < 2; ++h) {
-      mbar_init(bar_sfull(h), 1); mbar_init(bar_odone(h), 1);
-      mbar_init(bar_pready(h), TC_P_ARRIVALS); mbar_init(bar_pearly(h), TC_P_ARRIVALS);
+      mbar_init(bar_sfull(h), 1); mbar_init(bar_pready(h), 128); mbar_init(bar_odone(h), 1);
+      mbar_init(bar_token(h), 1);
     }
+    mbar_arrive(bar_token(0));     // head A's thread goes first
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (tid >= 64 && tid < 64 + DT_N) {
     const int e = tid - 64, ks = e & 7;
+    const uint64_t kstep = uint64_t(uint32_t(ks >> 2) * (TC_SLAB_BYTES >> 4) + uint32_t(ks & 3) * (32u >> 4));
     uint64_t d;
-    if (e < DT_K) {
-      d = desc_kmajor(sbase + TC_SMEM_Q + uint32_t(e >> 3) * TC_TILE_BYTES) +
-          uint64_t(uint32_t(ks >> 2) * (TC_SLAB_BYTES >> 4) + uint32_t(ks & 3) * (32u >> 4));
-    } else if (e < DT_V) {
-      d = desc_kmajor(sbase + TC_SMEM_K + uint32_t((e - DT_K) >> 3) * TC_TILE_BYTES) +
-          uint64_t(uint32_t(ks >> 2) * (TC_SLAB_BYTES >> 4) + uint32_t(ks & 3) * (32u >> 4));
-    } else {
-      d = desc_mnmajor(sbase + TC_SMEM_V + uint32_t((e - DT_V) >> 3) * TC_TILE_BYTES) + uint64_t(uint32_t(ks) * (2048u >> 4));
-    }
+    if (e < DT_K) d = desc_kmajor(sbase + TC_SMEM_Q + uint32_t(e >> 3) * TC_TILE_BYTES) + kstep;
+    else if (e < DT_V) d = desc_kmajor(sbase + TC_SMEM_K + uint32_t((e - DT_K) >> 3) * TC_TILE_BYTES) + kstep;
+    else d = desc_mnmajor(sbase + TC_SMEM_V + uint32_t((e - DT_V) >> 3) * TC_TILE_BYTES) + uint64_t(uint32_t(ks) * (2048u >> 4));
     dtab[e] = d;
   }
   if (warp == 0) {
@@ -204,10 +173,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t tmem = *tmem_slot;
 
   if (warp < 4) {
-    // control warpgroup (producer, MMA issuers, an idle warp) hands registers to the softmax warpgroups.
-    // The CTA owns the registers it was launched with (384 threads x 168) and no more: 4 warps x 88 +
-    // 8 warps x 208 stays within that pool; a sum beyond it would leave the last setmaxnreg.inc waiting
-    // for ever.
+    // control warpgroup (producer, MMA issuers, an idle warp) hands registers to the softmax warpgroups
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_REGS_CONTROL));
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -256,22 +222,20 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         mbar_wait(bar_vfull(j % TC_VSTAGES), (j / TC_VSTAGES) & 1, abort_flag, true);
     }
   } else if (warp <= 2) {
-    // ------------------------------------------------------------ MMA issuers (warp 1, warp 2)
-    // Two ways to run the CTA's pair of rows, chosen from the two bitmap rows (the same answer in both
-    // warps):
-    //  * alternating: warp 1 issues for both heads in the fixed order P V of A, next Q K^T of A, P V of
-    //    B, next Q K^T of B, which keeps the two softmax warpgroups half a period apart; best where
-    //    the heads visit (nearly) the same blocks.  Warp 2 does nothing.
-    //  * split: warp 1 issues for head A and warp 2 for head B, so a head never waits for the other
-    //    head's softmax on a block it does not visit; best where the lists differ.  Both walk the
-    //    union of the rows in the producer's order and take part in the hand-shake of every tile (a
-    //    tile the head does not visit is passed on as soon as it has landed), so the phase of a ring
-    //    stage can never run ahead of an issuer that skips it.
-    // Every K/V ring stage is released by two arrivals: one per issuer in split mode, both from warp 1
-    // in alternating mode.  These warps share their schedulers with the softmax warps, whose
-    // instruction issue is the bottleneck of the kernel: every instruction here is paid for there.
+    // ------------------------------------------------------------ MMA issuers (warp 1: head A, warp 2: head B)
+    // Both threads walk the union of the two bitmap rows in the producer's order and take part in the
+    // hand-shake of every ring stage (two arrivals free a stage; a tile the head does not visit is
+    // passed on as soon as it has landed), so the phase of a stage can never run ahead of a thread that
+    // skips it.  A CTA with a single head still runs both threads: warp 2 then only passes tiles on.
+    // Two ways to run a pair of rows, chosen from the two bitmap rows (the same answer in both warps):
+    //  * in step: a token goes back and forth, so the steps leave in the order A, B, A, B - P V of A and
+    //    the next Q K^T of A, then the same for B.  That keeps the two softmax warpgroups half a period
+    //    apart; best where the heads visit (nearly) the same blocks.  A thread's bookkeeping (ring
+    //    hand-shakes, bitmap walk, descriptor fetch) runs under the other thread's MMAs.
+    //  * free: no token; a head never waits for the other head's softmax on a block it does not visit;
+    //    best where the lists differ.
     // blocks of head A, of head B and of their union in this row (a lane per bitmap word, so the
-    // words arrive in one memory latency); split where the lists differ enough
+    // words arrive in one memory latency)
     int cnt_a = 0, cnt_b = 0, cnt_u = 0;
     for (int i = lane; i <= (r >> 5); i += 32) {
       const int last = r - (i << 5);
@@ -283,145 +247,67 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     cnt_b = __reduce_add_sync(0xffffffffu, cnt_b);
     cnt_u = __reduce_add_sync(0xffffffffu, cnt_u);
     if (lane == 0) {
-      const int me = warp - 1;
-      const bool split = hasB && (TC5_ALWAYS_SPLIT || 4 * cnt_u > 5 * max(cnt_a, cnt_b) || max(cnt_a, cnt_b) <= TC5_SPLIT_SHORT);
-      // descriptors differ from a base only in the 14-bit address field: one 64-bit add per operand
-      const uint64_t qdA = desc_kmajor(sbase + TC_SMEM_Q), qdB = desc_kmajor(sbase + TC_SMEM_Q + TC_TILE_BYTES);
-      const uint64_t kd0 = desc_kmajor(sbase + TC_SMEM_K), vd0 = desc_mnmajor(sbase + TC_SMEM_V);
-      // One head's share of an iteration: P V of the current block (if the head visits it) and Q K^T of
-      // the next one (if it visits that).  Everything that is not an MMA comes first - ring stages
-      // checked, the descriptors of all sixteen k-steps built - so that after the wait for P the
-      // instructions between the fence and the last MMA are MMAs only.
-      auto head_step = [&](int h, bool do_pv, bool do_qk, int vs_stage, int ks_stage, bool accumulate) {
-#if TC5_B2B
-        KSteps vd, qd, kd;
-        auto fetch = [&](int first, KSteps& o) {
-          const ulonglong2* src = reinterpret_cast<const ulonglong2*>(dtab + first);
+      const int h = warp - 1, mine = 1 << h;
+      const bool in_step = hasB && 4 * cnt_u <= 5 * max(cnt_a, cnt_b);
+      const uint32_t ts = tmem + (h == 0 ? 0u : 128u), to = tmem + (h == 0 ? 256u : 384u);
+      auto fetch = [&](int first, KSteps& o) {
+        const ulonglong2* src = reinterpret_cast<const ulonglong2*>(dtab + first);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { const ulonglong2 t = src[j]; o.d[2 * j] = t.x; o.d[2 * j + 1] = t.y; }
-        };
-        if (do_pv) fetch(DT_V + 8 * vs_stage, vd);
-        if (do_qk) { fetch(DT_Q + 8 * h, qd); fetch(DT_K + 8 * ks_stage, kd); }
-#else
-        const uint64_t vd = vd0 + uint64_t((vs_stage * TC_TILE_BYTES) >> 4), qd = h == 0 ? qdA : qdB,
-                       kd = kd0 + uint64_t((ks_stage * TC_TILE_BYTES) >> 4);
-#endif
-        const uint32_t ts = tmem + (h == 0 ? 0u : 128u), to = tmem + (h == 0 ? 256u : 384u);
-        // phase 0 (TC5_SPLIT_P only): the first six k-steps of P V; phase 1: the rest
-        return [=](int phase) {
-#if !TC5_B2B
-          (void)phase;
-          if (do_pv) mma_pv_group(to, ts, vd, accumulate ? 1u : 0u);
-          if (do_qk) { mma_qk_group(ts, qd, kd); tc_commit(bar_sfull(h)); }
-#else
-#if TC5_SPLIT_P
-          if (phase == 0) { if (do_pv) mma_pv_first6(to, ts, vd, accumulate ? 1u : 0u); return; }
-          if (do_pv) mma_pv_last2(to, ts, vd);
-#else
-          if (do_pv) mma_pv_x8(to, ts, vd, accumulate ? 1u : 0u);
-#endif
-          if (do_qk) { mma_qk_x8(ts, qd, kd); tc_commit(bar_sfull(h)); }
-#endif
-        };
+        for (int j = 0; j < 4; ++j) { const ulonglong2 t = src[j]; o.d[2 * j] = t.x; o.d[2 * j + 1] = t.y; }
       };
+      int step = 0;
+      auto take_token = [&]() { return !in_step || mbar_wait(bar_token(h), step & 1, abort_flag); };
+      auto pass_token = [&]() { if (in_step) mbar_arrive(bar_token(h ^ 1)); ++step; };
+
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       PairWalker wk; wk.init(rowA, rowB, r);
       int fl, nfl;
       int col = wk.next(fl);
       int i = 0;
-      if (!split && me == 0) {
-        // ---- alternating mode: warp 1 for both heads
-        int nblk[2] = {0, 0};     // P tiles consumed per head
-        if (ok && col >= 0) {
-          ok = mbar_wait(bar_kfull(0), 0, abort_flag);
-          tc_fence_after();
+      int np = 0;               // P tiles consumed
+      if (ok && col >= 0) {
+        ok = mbar_wait(bar_kfull(0), 0, abort_flag);
+        if (ok) {
+          KSteps qd, kd;
+          if (fl & mine) { fetch(DT_Q + 8 * h, qd); fetch(DT_K, kd); }
+          ok = take_token();
           if (ok) {
-            for (int h = 0; h < 2; ++h)
-              if (fl & (1 << h)) head_step(h, false, true, 0, 0, false)(1);
-            mbar_arrive(bar_kempty(0));
-            tc_commit(bar_kempty(0));
+            if (fl & mine) { tc_fence_after(); mma_qk_x8(ts, qd, kd); tc_commit(bar_sfull(h)); }
+            pass_token();
+            if (fl & mine) tc_commit(bar_kempty(0)); else mbar_arrive(bar_kempty(0));
           }
         }
-        while (ok && col >= 0) {
-          const int ncol = wk.next(nfl);
-          const int vs = i % TC_VSTAGES, nks = (i + 1) % TC_KSTAGES;
-          bool v_ready = false, nk_ready = false;
-          const int last_h = (fl & 2) ? 1 : 0;
-          const int nlast_h = (nfl & 2) ? 1 : 0;
-          for (int h = 0; h < 2 && ok; ++h) {
-            const bool do_pv = (fl & (1 << h)) != 0;
-            const bool do_qk = ncol >= 0 && (nfl & (1 << h)) != 0;
-            if (!do_pv && !do_qk) continue;
-            if (do_pv && !v_ready) { ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag); v_ready = true; }
-            if (ok && do_qk && !nk_ready) { ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag); nk_ready = true; }
-            if (!ok) break;
-            auto issue = head_step(h, do_pv, do_qk, vs, nks, nblk[h] > 0);
-            if (h == 0) TRACE(2, i, 0); else TRACE(2, i, 4);
-#if TC5_SPLIT_P
-            if (do_pv) {
-              ok = mbar_wait(bar_pearly(h), nblk[h] & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              issue(0);
-            }
-#endif
-            if (do_pv) ok = mbar_wait(bar_pready(h), nblk[h] & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            if (h == 0) TRACE(2, i, 1); else TRACE(2, i, 5);
-            issue(1);
-            if (h == 0) TRACE(2, i, 3); else TRACE(2, i, 7);
-            if (do_pv) {
-              ++nblk[h];
-              if (h == last_h) { mbar_arrive(bar_vempty(vs)); tc_commit(bar_vempty(vs)); }
-            }
-            if (do_qk && h == nlast_h) { mbar_arrive(bar_kempty(nks)); tc_commit(bar_kempty(nks)); }
-          }
-          col = ncol; fl = nfl; ++i;
-        }
-        tc_commit(bar_odone(0));
-        tc_commit(bar_odone(1));
-      } else if (split) {
-        // ---- split mode: this thread issues for head `me` and passes the other head's tiles on
-        const int h = me, mine = 1 << me;
-        int np = 0;               // P tiles consumed
-        if (ok && col >= 0) {
-          ok = mbar_wait(bar_kfull(0), 0, abort_flag);
-          if (ok) {
-            if (fl & mine) { tc_fence_after(); head_step(h, false, true, 0, 0, false)(1); tc_commit(bar_kempty(0)); }
-            else mbar_arrive(bar_kempty(0));
-          }
-        }
-        while (ok && col >= 0) {
-          const int ncol = wk.next(nfl);
-          const int vs = i % TC_VSTAGES, nks = (i + 1) % TC_KSTAGES;
-          const bool do_pv = (fl & mine) != 0, do_qk = ncol >= 0 && (nfl & mine) != 0;
-          ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag);
-          if (ok && ncol >= 0) ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag);
-          if (!ok) break;
-          if (do_pv || do_qk) {
-            auto issue = head_step(h, do_pv, do_qk, vs, nks, np > 0);
-#if TC5_SPLIT_P
-            if (do_pv) {
-              ok = mbar_wait(bar_pearly(h), np & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              issue(0);
-            }
-#endif
-            if (do_pv) ok = mbar_wait(bar_pready(h), np & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            issue(1);
-            if (do_pv) ++np;
-          }
-          // a stage this head used is released when its MMAs are done, one it skipped at once
-          if (do_pv) tc_commit(bar_vempty(vs)); else mbar_arrive(bar_vempty(vs));
-          if (ncol >= 0) { if (do_qk) tc_commit(bar_kempty(nks)); else mbar_arrive(bar_kempty(nks)); }
-          col = ncol; fl = nfl; ++i;
-        }
-        tc_commit(bar_odone(h));
       }
+      while (ok && col >= 0) {
+        const int ncol = wk.next(nfl);
+        const int vs = i % TC_VSTAGES, nks = (i + 1) % TC_KSTAGES;
+        const bool do_pv = (fl & mine) != 0, do_qk = ncol >= 0 && (nfl & mine) != 0;
+        ok = mbar_wait(bar_vfull(vs), (i / TC_VSTAGES) & 1, abort_flag);
+        if (ok && ncol >= 0) ok = mbar_wait(bar_kfull(nks), ((i + 1) / TC_KSTAGES) & 1, abort_flag);
+        if (!ok) break;
+        // everything that is not an MMA comes first, so that between the wait for P and the last MMA of
+        // the step there are MMAs only
+        KSteps vd, qd, kd;
+        if (do_pv) fetch(DT_V + 8 * vs, vd);
+        if (do_qk) { fetch(DT_Q + 8 * h, qd); fetch(DT_K + 8 * nks, kd); }
+        if (h == 0) TRACE(2, i, 0);
+        ok = take_token();
+        if (ok && do_pv) ok = mbar_wait(bar_pready(h), np & 1, abort_flag);
+        if (!ok) break;
+        if (do_pv || do_qk) {
+          tc_fence_after();
+          if (h == 0) TRACE(2, i, 1);
+          if (do_pv) { mma_pv_x8(to, ts, vd, np > 0 ? 1u : 0u); ++np; }
+          if (do_qk) { mma_qk_x8(ts, qd, kd); tc_commit(bar_sfull(h)); }
+          if (h == 0) TRACE(2, i, 3);
+        }
+        pass_token();
+        // a stage this head used is released when its MMAs are done, one it skipped at once
+        if (do_pv) tc_commit(bar_vempty(vs)); else mbar_arrive(bar_vempty(vs));
+        if (ncol >= 0) { if (do_qk) tc_commit(bar_kempty(nks)); else mbar_arrive(bar_kempty(nks)); }
+        col = ncol; fl = nfl; ++i;
+      }
+      tc_commit(bar_odone(h));
     }
   }
   } else {
@@ -461,11 +347,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mask_after(s2, row - 64);
           mask_after(s3, row - 96);
         }
-#if TC5_MAX_TREE
-        const float mx = row_max4(s0, s1, s2, s3);
-#else
         const float mx = fmaxf(fmaxf(row_max(s0), row_max(s1)), fmaxf(row_max(s2), row_max(s3)));
-#endif
         const float mb = mx * p.scale_log2;
         if (lane == 0 && quarter == 0) TRACE(h, k, 5);
         float alpha = 1.f;
@@ -492,31 +374,16 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         // P = 2^(s*scale - m) as bf16 over the first 64 columns of the S region
         float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
         uint32_t pk[16];
-        exp_pack_mixed<TC5_POLY_PAIRS>(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tS + 0, pk);
-        exp_pack_mixed<TC5_POLY_PAIRS>(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tS + 16, pk);
-        exp_pack_mixed<TC5_POLY_PAIRS>(s2, p.scale_log2, m_used, pk, l2); tmem_st16(tS + 32, pk);
-#if TC5_SPLIT_P
-        tc_wait_st();
-        tc_fence_before();
-#if TC5_WARP_ARRIVE
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_pearly(h));
-#else
-        mbar_arrive(bar_pearly(h));
-#endif
-#endif
-        exp_pack_mixed<TC5_POLY_PAIRS>(s3, p.scale_log2, m_used, pk, l3); tmem_st16(tS + 48, pk);
+        exp_pack(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tS + 0, pk);
+        exp_pack(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tS + 16, pk);
+        exp_pack(s2, p.scale_log2, m_used, pk, l2); tmem_st16(tS + 32, pk);
+        exp_pack(s3, p.scale_log2, m_used, pk, l3); tmem_st16(tS + 48, pk);
         l_sum += (l0 + l1) + (l2 + l3);
         if (lane == 0 && quarter == 0) TRACE(h, k, 3);
         tc_wait_st();
         if (lane == 0 && quarter == 0) TRACE(h, k, 6);
         tc_fence_before();
-#if TC5_WARP_ARRIVE
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_pready(h));
-#else
         mbar_arrive(bar_pready(h));
-#endif
         if (lane == 0 && quarter == 0) TRACE(h, k, 4);
       }
       // ---- epilogue

@@ -126,21 +126,6 @@ __device__ __forceinline__ float row_max(const uint32_t (&r)[32]) {
   }
   return max3(fmaxf(a, b), __uint_as_float(r[30]), __uint_as_float(r[31]));
 }
-// maximum of a 128-element row held as four 32-register chunks: element-wise across the chunks first
-// (32 independent chains), then a 3-input tree - many short chains instead of eight long ones
-__device__ __forceinline__ float row_max4(const uint32_t (&a)[32], const uint32_t (&b)[32], const uint32_t (&c)[32],
-                                          const uint32_t (&d)[32]) {
-  float t[32];
-#pragma unroll
-  for (int j = 0; j < 32; ++j)
-    t[j] = fmaxf(max3(__uint_as_float(a[j]), __uint_as_float(b[j]), __uint_as_float(c[j])), __uint_as_float(d[j]));
-  float u[11];
-#pragma unroll
-  for (int j = 0; j < 10; ++j) u[j] = max3(t[3 * j], t[3 * j + 1], t[3 * j + 2]);
-  u[10] = fmaxf(t[30], t[31]);
-  const float v0 = max3(u[0], u[1], u[2]), v1 = max3(u[3], u[4], u[5]), v2 = max3(u[6], u[7], u[8]);
-  return max3(max3(v0, v1, v2), u[9], u[10]);
-}
 // two fp32 lanes in one 64-bit register (packed fp32x2 arithmetic of sm_100)
 __device__ __forceinline__ unsigned long long f2_pack(float lo, float hi) {
   unsigned long long d;
@@ -177,53 +162,6 @@ __device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], float scale, f
     float y0, y1;
     f2_unpack(f2_fma(x, sc2, nm2), y0, y1);
     const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-    acc[(j >> 1) & 3] = f2_add(acc[(j >> 1) & 3], f2_pack(p0, p1));
-    pk[j >> 1] = bf16x2_from(p0, p1);
-  }
-  float a0, a1;
-  f2_unpack(f2_add(f2_add(acc[0], acc[1]), f2_add(acc[2], acc[3])), a0, a1);
-  sum += a0 + a1;
-}
-
-// The same with POLY of every 8 element pairs taken off the exponential unit: their 2^x comes from a
-// Cody-Waite range reduction and a degree-3 polynomial on the FMA pipe (relative error 7.5e-5, far
-// below the bf16 rounding of P), so the MUFU sees (8 - POLY)/8 of the exponentials.
-//   u = sat((x + 120) / 128) in [0,1]            x = s*scale - m is at most 2^8 above zero; below -120 -> 2^-120
-//   n = round(128u - 120) by the 1.5*2^23 trick; f = 128u - 120 - n in [-0.5, 0.5]
-//   2^x = p(f) * 2^n: n is added to the exponent field of p(f)
-template <int POLY>
-__device__ __forceinline__ void exp_pack_mixed(const uint32_t (&r)[32], float scale, float m, uint32_t (&pk)[16], float& sum) {
-  const unsigned long long sc2 = f2_pack(scale, scale), nm2 = f2_pack(-m, -m);
-  const float sc128 = scale * 0.0078125f, b128 = (120.f - m) * 0.0078125f;
-  constexpr float MAGIC = 12582912.f - 120.f;      // 1.5 * 2^23 - 120
-  const unsigned long long k128 = f2_pack(128.f, 128.f), kmag = f2_pack(MAGIC, MAGIC), kneg = f2_pack(-1.f, -1.f);
-  const unsigned long long c0 = f2_pack(0.99992806f, 0.99992806f), c1 = f2_pack(0.69326097f, 0.69326097f),
-                           c2 = f2_pack(0.24261113f, 0.24261113f), c3 = f2_pack(0.05517167f, 0.05517167f);
-  unsigned long long acc[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-  for (int j = 0; j < 32; j += 2) {
-    float p0, p1;
-    if (((j >> 1) & 7) < POLY) {
-      const float u0 = __saturatef(fmaf(__uint_as_float(r[j]), sc128, b128));
-      const float u1 = __saturatef(fmaf(__uint_as_float(r[j + 1]), sc128, b128));
-      const unsigned long long u = f2_pack(u0, u1);
-      const unsigned long long xf = f2_fma(u, k128, kmag);          // MAGIC + n (n in the low mantissa bits)
-      const unsigned long long c = f2_fma(xf, kneg, kmag);          // -(120 + n)
-      const unsigned long long f = f2_fma(u, k128, c);
-      unsigned long long pl = f2_fma(f, c3, c2);
-      pl = f2_fma(pl, f, c1);
-      pl = f2_fma(pl, f, c0);
-      float q0, q1, x0, x1;
-      f2_unpack(pl, q0, q1);
-      f2_unpack(xf, x0, x1);
-      p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(x0) << 23));
-      p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(x1) << 23));
-    } else {
-      const unsigned long long x = f2_pack(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-      float y0, y1;
-      f2_unpack(f2_fma(x, sc2, nm2), y0, y1);
-      p0 = fast_exp2(y0); p1 = fast_exp2(y1);
-    }
     acc[(j >> 1) & 3] = f2_add(acc[(j >> 1) & 3], f2_pack(p0, p1));
     pk[j >> 1] = bf16x2_from(p0, p1);
   }
@@ -347,26 +285,9 @@ __device__ __forceinline__ void mma_pv_group(uint32_t o_tmem, uint32_t p_tmem, u
 }
 
 // The same products with every descriptor prepared BEFORE the first tcgen05.mma, so that the eight
-// instructions leave the issuing thread back to back.  The thread shares its scheduler with softmax
-// warps that always have something to issue: an instruction between two MMAs waits ~10-20 clk for an
-// issue slot, and the tensor pipe does not take the next MMA while it waits - four such instructions
-// per k-step made a Q K^T group take ~800 clk instead of 512.
+// instructions leave the issuing thread back to back (the attention kernel keeps the descriptors of
+// every tile in a shared-memory table).
 struct KSteps { uint64_t d[8]; };
-// K-major operand: steps 0-3 walk the first 64-element slab in 32-byte strides, 4-7 the second
-__device__ __forceinline__ void ksteps_kmajor(uint64_t base, KSteps& o) {
-  const uint32_t lo = static_cast<uint32_t>(base), hi = static_cast<uint32_t>(base >> 32);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t off = uint32_t(i >> 2) * (TC_SLAB_BYTES >> 4) + uint32_t(i & 3) * (32u >> 4);
-    o.d[i] = (uint64_t(hi) << 32) | uint64_t(lo + off);
-  }
-}
-// MN-major operand (V): 16 keys = 2048 bytes per step
-__device__ __forceinline__ void ksteps_mnmajor(uint64_t base, KSteps& o) {
-  const uint32_t lo = static_cast<uint32_t>(base), hi = static_cast<uint32_t>(base >> 32);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) o.d[i] = (uint64_t(hi) << 32) | uint64_t(lo + uint32_t(i) * (2048u >> 4));
-}
 __device__ __forceinline__ void mma_qk_x8(uint32_t d_tmem, const KSteps& a, const KSteps& b) {
   asm volatile(
       "{\n\t.reg .pred pz, po;\n\t"
@@ -401,33 +322,6 @@ __device__ __forceinline__ void mma_pv_x8(uint32_t o_tmem, uint32_t p_tmem, cons
         "r"(p_tmem), "r"(p_tmem + 8u), "r"(p_tmem + 16u), "r"(p_tmem + 24u), "r"(p_tmem + 32u), "r"(p_tmem + 40u),
         "r"(p_tmem + 48u), "r"(p_tmem + 56u),
         "l"(v.d[0]), "l"(v.d[1]), "l"(v.d[2]), "l"(v.d[3]), "l"(v.d[4]), "l"(v.d[5]), "l"(v.d[6]), "l"(v.d[7])
-      : "memory");
-}
-
-// the same product in two parts, for a P tile that becomes ready in two parts: k-steps 0-5 (the first
-// 96 keys), then k-steps 6-7
-__device__ __forceinline__ void mma_pv_first6(uint32_t o_tmem, uint32_t p_tmem, const KSteps& v, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred pa, po;\n\t"
-      "setp.ne.b32 pa, %2, 0;\n\tsetp.eq.b32 po, 0, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %9, %1, pa;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %10, %1, po;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %11, %1, po;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %12, %1, po;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %13, %1, po;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%8], %14, %1, po;\n\t}"
-      ::"r"(o_tmem), "r"(TC_IDESC_PV), "r"(acc),
-        "r"(p_tmem), "r"(p_tmem + 8u), "r"(p_tmem + 16u), "r"(p_tmem + 24u), "r"(p_tmem + 32u), "r"(p_tmem + 40u),
-        "l"(v.d[0]), "l"(v.d[1]), "l"(v.d[2]), "l"(v.d[3]), "l"(v.d[4]), "l"(v.d[5])
-      : "memory");
-}
-__device__ __forceinline__ void mma_pv_last2(uint32_t o_tmem, uint32_t p_tmem, const KSteps& v) {
-  asm volatile(
-      "{\n\t.reg .pred po;\n\t"
-      "setp.eq.b32 po, 0, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %4, %1, po;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %5, %1, po;\n\t}"
-      ::"r"(o_tmem), "r"(TC_IDESC_PV), "r"(p_tmem + 48u), "r"(p_tmem + 56u), "l"(v.d[6]), "l"(v.d[7])
       : "memory");
 }
 
