@@ -52,10 +52,12 @@ constexpr int DT_Q = 0, DT_K = 16, DT_V = DT_K + 8 * TC_KSTAGES, DT_N = DT_V + 8
 static_assert(TC_SMEM_DTAB + DT_N * 8 <= TC_SMEM_Q, "descriptor table does not fit the control region");
 
 // Timing probe, compiled in only with -DSPF_TC5_TRACE: clock64() stamps of the first CTA's
-// first 64 iterations, [role: softmax A, softmax B, MMA issuer A][iteration][slot].
+// first 63 iterations, [role: softmax A, softmax B, MMA issuer A][iteration][slot]; [2][63][*] holds the
+// CTA-level stamps (entry, set-up done, Q landed, first Q K^T issued, epilogue begin / end, first K
+// requested, exit).
 #ifdef SPF_TC5_TRACE
 __device__ long long g_tc5_trace[3][64][8];
-#define TRACE(role, it, slot) do { if (blockIdx.x == 0 && (it) < 64) g_tc5_trace[role][it][slot] = clock64(); } while (0)
+#define TRACE(role, it, slot) do { if (blockIdx.x == SPF_TC5_TRACE && (it) < 64) g_tc5_trace[role][it][slot] = clock64(); } while (0)
 #else
 #define TRACE(role, it, slot) do {} while (0)
 #endif
@@ -142,6 +144,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t* rowA = p.bitmap + (int64_t(hA) * p.nb + r) * p.nbw;
   const uint32_t* rowB = hasB ? p.bitmap + (int64_t(hB) * p.nb + r) * p.nbw : nullptr;
 
+  if (tid == 0) TRACE(2, 63, 0);
   if (tid == 0) {
     mbar_init(bar_q, 1);
     for (int s = 0; s < TC_KSTAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_kempty(s), 2); }
@@ -171,6 +174,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (tid == 0) TRACE(2, 63, 1);
 
   if (warp < 4) {
     // control warpgroup (producer, MMA issuers, an idle warp) hands registers to the softmax warpgroups
@@ -208,6 +212,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       int col = wk.next(fl);
       bool ok = true;
       if (col >= 0) { ok = load_k(0, col); k_issued = ok ? 1 : 0; }
+      TRACE(2, 63, 6);
       while (ok && col >= 0) {
         const int ncol = wk.next(fl);
         if (ncol >= 0) { ok = load_k(i + 1, ncol); if (ok) k_issued = i + 2; }
@@ -260,6 +265,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       auto pass_token = [&]() { if (in_step) mbar_arrive(bar_token(h ^ 1)); ++step; };
 
       bool ok = mbar_wait(bar_q, 0, abort_flag);
+      if (h == 0) TRACE(2, 63, 2);
       PairWalker wk; wk.init(rowA, rowB, r);
       int fl, nfl;
       int col = wk.next(fl);
@@ -273,6 +279,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ok = take_token();
           if (ok) {
             if (fl & mine) { tc_fence_after(); mma_qk_x8(ts, qd, kd); tc_commit(bar_sfull(h)); }
+            if (h == 0) TRACE(2, 63, 3);
             pass_token();
             if (fl & mine) tc_commit(bar_kempty(0)); else mbar_arrive(bar_kempty(0));
           }
@@ -387,6 +394,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0 && quarter == 0) TRACE(h, k, 4);
       }
       // ---- epilogue
+      if (h == 0 && lane == 0 && quarter == 0) TRACE(2, 63, 4);
       const int tok = row0 + row;
       __nv_bfloat16* orow = p.out + (int64_t(tok) * p.n_q_heads + head) * TC_D;
       if (ok && k > 0) ok = mbar_wait(bar_odone(h), 0, abort_flag);
@@ -415,6 +423,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
         }
       }
+      if (h == 0 && lane == 0 && quarter == 0) TRACE(2, 63, 5);
     }
   }
   __syncwarp();
@@ -424,6 +433,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
   }
+  if (tid == 0) TRACE(2, 63, 7);
 }
 
 // ---------------------------------------------------------------- host side
