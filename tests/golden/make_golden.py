@@ -216,6 +216,12 @@ SCALE_CASES = {
         wl=AttentionWorkload("llama_32k_diffuse", 98, 32768, 32, 8, num_layers=15, rope_theta=500000.0,
                              queryaware_threshold=0.15),
         lookup="shipped", layers=[14], score_heads=[16, 17, 18, 19]),
+    # Llama-3.1-70B head layout (64 query / 8 KV heads, groups of 8) at 8K tokens; scores kept for KV group 1,
+    # whose first head becomes the pivot of shared cluster 1
+    "llama70b_8k": dict(
+        wl=AttentionWorkload("llama70b_8k", 100, 8192, 64, 8, num_layers=2, rope_theta=500000.0,
+                             queryaware_threshold=0.17, fallback_threshold=1e9, similarity_threshold=0.9),
+        lookup=dict(num_clusters=4, shared=[1]), layers=[0, 1], score_heads=[8, 9, 10, 11, 12, 13, 14, 15]),
     # 128K tokens, one KV group of four query heads; the threshold makes exactly one of them query-aware
     "group_128k": dict(
         wl=AttentionWorkload("group_128k", 99, 131072, 4, 1, num_layers=1, num_head_clusters=1,

@@ -72,7 +72,7 @@ class GoldenCase:
 
 
 # ----------------------------------------------------------------------------- benchmark-sized cases
-SCALE_CASE_NAMES = ["qa_8k", "mixed_8k", "qwen_8k", "llama_32k", "llama_32k_diffuse", "group_128k"]
+SCALE_CASE_NAMES = ["qa_8k", "mixed_8k", "qwen_8k", "llama70b_8k", "llama_32k", "llama_32k_diffuse", "group_128k"]
 
 
 def shipped_lookup_path():
