@@ -1,8 +1,10 @@
 // Block-sparse causal flash attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA)
 // for block_size = head_dim = 128.
 //
-// One CTA owns one query block row of up to TWO query heads of the same KV group, so every K/V
-// tile fetched by TMA serves both heads (GQA reuse); the two heads ping-pong on the tensor pipe.
+// One CTA runs TWO streams that share their K/V tiles: one query block row of two query heads of the
+// same KV group (GQA reuse), or - for the last head of an odd-sized group - two consecutive query block
+// rows of that head (neighbouring rows visit nearly the same key blocks).  Every K/V tile fetched by TMA
+// serves both streams, which ping-pong on the tensor pipe.  Below, "head A / head B" names the streams.
 //
 //   warp 0      TMA producer: Q tiles once, then K and V tiles of the union of both heads' bitmap
 //               rows through a 3-deep K ring and a 2-deep V ring (cp.async.bulk.tensor, 128-byte
@@ -65,25 +67,26 @@ __device__ long long g_tc5_trace[3][64][8];
 struct Tc5Params {
   __nv_bfloat16* out;
   const uint32_t* bitmap;
-  int n_tokens, n_q_heads, n_kv_heads, group, pairs, nb, nbw;
+  int n_tokens, n_q_heads, n_kv_heads, group, pairs, nb, nbw;   // pairs: whole head pairs per KV group
   float scale_log2;
 };
 
 // Walks the union of two bitmap rows in ascending column order; flags bit h = head h visits it.
 struct PairWalker {
   const uint32_t* wa; const uint32_t* wb;
-  int row, nwords, w;
+  int ra, rb, nwords, w;       // last causal column block of stream A / B
   uint32_t ca, cb;
-  __device__ uint32_t lim(int wi, uint32_t x) const {
+  __device__ static uint32_t lim(int row, int wi, uint32_t x) {
     const int last = row - (wi << 5);
-    return last >= 31 ? x : (x & ((2u << last) - 1u));
+    return last >= 31 ? x : (last < 0 ? 0u : (x & ((2u << last) - 1u)));
   }
   __device__ void load(int wi) {
-    ca = wa ? lim(wi, __ldg(wa + wi)) : 0u;
-    cb = wb ? lim(wi, __ldg(wb + wi)) : 0u;
+    ca = wa ? lim(ra, wi, __ldg(wa + wi)) : 0u;
+    cb = wb ? lim(rb, wi, __ldg(wb + wi)) : 0u;
   }
-  __device__ void init(const uint32_t* a, const uint32_t* b, int row_) {
-    wa = a; wb = b; row = row_; nwords = (row_ >> 5) + 1; w = 0;
+  __device__ void init(const uint32_t* a, int row_a, const uint32_t* b, int row_b) {
+    wa = a; wb = b; ra = row_a; rb = row_b; w = 0;
+    nwords = (max(a ? row_a : 0, b ? row_b : 0) >> 5) + 1;
     load(0);
   }
   __device__ int next(int& flags) {
@@ -133,16 +136,27 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // CTAs that run at the same time belong to the same KV head (its K/V stream stays in L2);
   // within a KV head the heavy (late) query blocks go first
+  // Per KV head: nb * pairs CTAs with two heads and one row each, then - if the group size is odd -
+  // ceil(nb / 2) CTAs with the last head and two rows each.
   int bid = blockIdx.x;
-  const int pair = bid % p.pairs; bid /= p.pairs;
-  const int r = p.nb - 1 - (bid % p.nb);
-  const int kvh = bid / p.nb;
-  const int hA = kvh * p.group + pair * 2;
-  const bool hasB = (pair * 2 + 1) < p.group;
-  const int hB = hasB ? hA + 1 : -1;
-  const int row0 = r * TC_BS;
-  const uint32_t* rowA = p.bitmap + (int64_t(hA) * p.nb + r) * p.nbw;
-  const uint32_t* rowB = hasB ? p.bitmap + (int64_t(hB) * p.nb + r) * p.nbw : nullptr;
+  const int n_rp = (p.group & 1) ? (p.nb + 1) >> 1 : 0;
+  const int per_kvh = p.nb * p.pairs + n_rp;
+  const int kvh = bid / per_kvh;
+  bid -= kvh * per_kvh;
+  int hA, hB, rA, rB;
+  if (bid < p.nb * p.pairs) {
+    const int pair = bid % p.pairs;
+    rA = rB = p.nb - 1 - bid / p.pairs;
+    hA = kvh * p.group + pair * 2; hB = hA + 1;
+  } else {
+    const int rp = n_rp - 1 - (bid - p.nb * p.pairs);
+    hA = kvh * p.group + p.group - 1;
+    rA = 2 * rp; rB = 2 * rp + 1;
+    hB = rB < p.nb ? hA : -1;
+  }
+  const bool hasB = hB >= 0;
+  const uint32_t* rowA = p.bitmap + (int64_t(hA) * p.nb + rA) * p.nbw;
+  const uint32_t* rowB = hasB ? p.bitmap + (int64_t(hB) * p.nb + rB) * p.nbw : nullptr;
 
   if (tid == 0) TRACE(2, 63, 0);
   if (tid == 0) {
@@ -185,8 +199,8 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_expect_tx(bar_q, (hasB ? 2u : 1u) * TC_TILE_BYTES);
       for (int h = 0; h < (hasB ? 2 : 1); ++h) {
         const uint32_t dst = sbase + TC_SMEM_Q + h * TC_TILE_BYTES;
-        tma_load_3d(dst, &map_q, bar_q, 0, row0, hA + h);
-        tma_load_3d(dst + TC_SLAB_BYTES, &map_q, bar_q, 64, row0, hA + h);
+        tma_load_3d(dst, &map_q, bar_q, 0, (h == 0 ? rA : rB) * TC_BS, h == 0 ? hA : hB);
+        tma_load_3d(dst + TC_SLAB_BYTES, &map_q, bar_q, 64, (h == 0 ? rA : rB) * TC_BS, h == 0 ? hA : hB);
       }
       auto load_k = [&](int i, int col) -> bool {
         const int s = i % TC_KSTAGES;
@@ -207,7 +221,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         return true;
       };
       // K runs one column ahead of V: K(i+1) is requested before V(i)
-      PairWalker wk; wk.init(rowA, rowB, r);
+      PairWalker wk; wk.init(rowA, rA, rowB, rB);
       int fl, i = 0, k_issued = 0, v_issued = 0;
       int col = wk.next(fl);
       bool ok = true;
@@ -242,10 +256,9 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // blocks of head A, of head B and of their union in this row (a lane per bitmap word, so the
     // words arrive in one memory latency)
     int cnt_a = 0, cnt_b = 0, cnt_u = 0;
-    for (int i = lane; i <= (r >> 5); i += 32) {
-      const int last = r - (i << 5);
-      const uint32_t m = last >= 31 ? 0xffffffffu : ((2u << last) - 1u);
-      const uint32_t wa = __ldg(rowA + i) & m, wb = hasB ? (__ldg(rowB + i) & m) : 0u;
+    for (int i = lane; i <= (max(rA, rB) >> 5); i += 32) {
+      const uint32_t wa = PairWalker::lim(rA, i, __ldg(rowA + i));
+      const uint32_t wb = hasB ? PairWalker::lim(rB, i, __ldg(rowB + i)) : 0u;
       cnt_a += __popc(wa); cnt_b += __popc(wb); cnt_u += __popc(wa | wb);
     }
     cnt_a = __reduce_add_sync(0xffffffffu, cnt_a);
@@ -266,7 +279,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       if (h == 0) TRACE(2, 63, 2);
-      PairWalker wk; wk.init(rowA, rowB, r);
+      PairWalker wk; wk.init(rowA, rA, rowB, rB);
       int fl, nfl;
       int col = wk.next(fl);
       int i = 0;
@@ -324,6 +337,8 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;           // query row within the block
     const int head = h == 0 ? hA : hB;
+    const int r = h == 0 ? rA : rB;                // this stream's query block row
+    const int row0 = r * TC_BS;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const uint32_t tS = tmem + lane_base + uint32_t(h * 128);
     const uint32_t tO = tmem + lane_base + uint32_t(256 + h * 128);
@@ -331,7 +346,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     int k = 0;
     bool ok = head >= 0;
     if (ok) {
-      PairWalker wk; wk.init(h == 0 ? rowA : rowB, nullptr, r);
+      PairWalker wk; wk.init(h == 0 ? rowA : rowB, r, nullptr, 0);
       int fl;
       for (int col = wk.next(fl); col >= 0 && ok; col = wk.next(fl), ++k) {
         if (lane == 0 && quarter == 0) TRACE(h, k, 0);
@@ -449,12 +464,12 @@ int sparse_attention_tc5(const AttnParams& a, int n_kv_heads, cudaStream_t st) {
     return SPF_ERR_SHAPE;
   Tc5Params p;
   p.out = a.out; p.bitmap = a.bitmap; p.n_tokens = a.n_tokens; p.n_q_heads = a.n_q_heads;
-  p.n_kv_heads = n_kv_heads; p.group = a.group; p.pairs = (a.group + 1) / 2; p.nb = a.nb; p.nbw = a.nbw;
+  p.n_kv_heads = n_kv_heads; p.group = a.group; p.pairs = a.group / 2; p.nb = a.nb; p.nbw = a.nbw;
   p.scale_log2 = a.scale_log2;
   cudaError_t e = cudaFuncSetAttribute(sparse_attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        int(TC_SMEM_TOTAL));
   if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
-  const unsigned grid = unsigned(a.nb) * unsigned(n_kv_heads) * unsigned(p.pairs);
+  const unsigned grid = unsigned(n_kv_heads) * (unsigned(a.nb) * unsigned(p.pairs) + ((a.group & 1) ? unsigned(a.nb + 1) / 2u : 0u));
   sparse_attn_tc5_kernel<<<grid, TC_THREADS, TC_SMEM_TOTAL, st>>>(mq, mk, mv, p);
   return check_launch();
 }

@@ -88,8 +88,9 @@ __device__ CoverResult cover_select(Load load, int n, float thr, int rule, int s
     __syncthreads();
     for (int b = threadIdx.x; b < nbins; b += blockDim.x) { sh->cnt[b] = 0; sh->sum[b] = 0ull; }
     __syncthreads();
-    // four elements per thread and trip, loaded before any is used (one load in flight per thread
-    // leaves the loop waiting on memory); elements past the end read as zero, which is skipped.
+    // eight elements (four 16-byte vectors on the contiguous path) per thread and trip, loaded before any
+    // is used (one load in flight per thread leaves the loop waiting on memory); elements past the end
+    // read as zero, which is skipped.
     // (Adding up the lanes that share a bin with match_any before touching the histogram was measured
     // slower than the plain shared-memory atomics on the token profiles: 312 against 191 us for 64
     // vectors of 128K elements.)
@@ -125,15 +126,15 @@ __device__ CoverResult cover_select(Load load, int n, float thr, int rule, int s
         for (int u = 0; u < 4; ++u) { take(xs[u].x); take(xs[u].y); take(xs[u].z); take(xs[u].w); }
       }
     } else {
-      for (int i0 = threadIdx.x; i0 < n; i0 += 4 * blockDim.x) {
-        float xs[4];
+      for (int i0 = threadIdx.x; i0 < n; i0 += 8 * blockDim.x) {
+        float xs[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
           const int i = i0 + u * blockDim.x;
           xs[u] = i < n ? load(i) : 0.f;
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) take(xs[u]);
+        for (int u = 0; u < 8; ++u) take(xs[u]);
       }
     }
     if (RUN_LENGTH && run_cnt) { atomicAdd(&sh->cnt[run_bin], run_cnt); atomicAdd(&sh->sum[run_bin], run_fx); }

@@ -347,6 +347,9 @@ def sparse_attention(q, k, v, bitmap, block_size, softmax_scale, flags=None, slo
     return out
 
 
+_decode_scratch = {}
+
+
 def decode_attention(q, k, v, softmax_scale, out=None):
     """q ``[H,D]``, k/v ``[Nk,Hkv,D]`` views -> ``[H,D]`` (one decode step, dense attention)."""
     lib = load()
@@ -358,7 +361,15 @@ def decode_attention(q, k, v, softmax_scale, out=None):
         raise SpfError(f"decode cache shapes {tuple(k.shape)}/{tuple(v.shape)} do not match query {tuple(q.shape)}")
     if out is None:
         out = torch.empty(h, d, dtype=torch.bfloat16, device=q.device)
-    scratch = torch.empty(lib.spf_decode_scratch_bytes(nk, h, k.shape[1], d), dtype=torch.uint8, device=q.device)
+    # split-K partials: one buffer per (device, stream), grown on demand and reused by every decode step
+    # (calls on one stream are ordered: the merge kernel has consumed the partials before the next call's
+    # first kernel starts)
+    need = lib.spf_decode_scratch_bytes(nk, h, k.shape[1], d)
+    key = (q.device, _stream())
+    scratch = _decode_scratch.get(key)
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=q.device)
+        _decode_scratch[key] = scratch
     kp, vp = _nhd(k), _nhd(v)
     _check(lib.spf_decode_attention(q.data_ptr(), q.stride(0), kp[0], kp[1], kp[2], vp[0], vp[1], vp[2], nk, h,
                                     k.shape[1], d, float(softmax_scale), out.data_ptr(), scratch.data_ptr(),
