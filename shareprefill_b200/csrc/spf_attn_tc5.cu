@@ -48,7 +48,10 @@ constexpr uint32_t TC_SMEM_Q = 1024;
 constexpr uint32_t TC_SMEM_K = TC_SMEM_Q + 2 * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_V = TC_SMEM_K + TC_KSTAGES * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_V + TC_VSTAGES * TC_TILE_BYTES;   // 225 KiB of the 227 KiB limit
-constexpr float TC_RESCALE_LOG2 = 8.0f;
+// O is rescaled only when a row's maximum moved by more than this (in log2 units) above the reference
+// point in use; P = 2^(s - reference) then reaches at most 2^24, far inside the range of bf16 and of the
+// fp32 accumulators, and the final normalisation uses the same reference, so the result is exact
+constexpr float TC_RESCALE_LOG2 = 24.0f;
 // descriptor table: the eight k-step descriptors of Q_A, Q_B, every K stage and every V stage
 constexpr int DT_Q = 0, DT_K = 16, DT_V = DT_K + 8 * TC_KSTAGES, DT_N = DT_V + 8 * TC_VSTAGES;
 static_assert(TC_SMEM_DTAB + DT_N * 8 <= TC_SMEM_Q, "descriptor table does not fit the control region");
@@ -104,7 +107,8 @@ struct PairWalker {
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, const Tc5Params p) {
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                       const Tc5Params p) {
   // once several waits have run out the kernel is not making progress: later CTAs do nothing
   if (*reinterpret_cast<volatile unsigned int*>(&g_tc5_timeouts) > 16u) return;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -159,6 +163,7 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t* rowB = hasB ? p.bitmap + (int64_t(hB) * p.nb + rB) * p.nbw : nullptr;
 
   if (tid == 0) TRACE(2, 63, 0);
+  if (tid == 32) { tma_prefetch_map(&map_q); tma_prefetch_map(&map_k); tma_prefetch_map(&map_v); tma_prefetch_map(&map_o); }
   if (tid == 0) {
     mbar_init(bar_q, 1);
     for (int s = 0; s < TC_KSTAGES; ++s) { mbar_init(bar_kfull(s), 1); mbar_init(bar_kempty(s), 2); }
@@ -410,9 +415,12 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       // ---- epilogue
       if (h == 0 && lane == 0 && quarter == 0) TRACE(2, 63, 4);
-      const int tok = row0 + row;
-      __nv_bfloat16* orow = p.out + (int64_t(tok) * p.n_q_heads + head) * TC_D;
       if (ok && k > 0) ok = mbar_wait(bar_odone(h), 0, abort_flag);
+      // O / l as bf16 into this head's Q tile (all its Q K^T products are done), in the swizzled layout
+      // of a TMA tile; then one thread stores the two 64-column slabs.  Rows past the end of the
+      // sequence are clipped by the copy.
+      const uint32_t stage = sbase + TC_SMEM_Q + uint32_t(h) * TC_TILE_BYTES;
+      if (ok && k == 0) ok = mbar_wait(bar_q, 0, abort_flag);   // a row that visits nothing: the Q copy may still be landing
       if (ok) {
         tc_fence_after();
         const float inv = (k > 0 && l_sum > 0.f) ? 1.f / l_sum : 0.f;
@@ -425,18 +433,24 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.f;
           }
-          if (tok < p.n_tokens) {
+          const uint32_t rbase = stage + uint32_t(c >> 1) * TC_SLAB_BYTES + uint32_t(row) * 128u;
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 o;
-              o.x = pack2_bf16(v[j] * inv, v[j + 1] * inv);
-              o.y = pack2_bf16(v[j + 2] * inv, v[j + 3] * inv);
-              o.z = pack2_bf16(v[j + 4] * inv, v[j + 5] * inv);
-              o.w = pack2_bf16(v[j + 6] * inv, v[j + 7] * inv);
-              *reinterpret_cast<uint4*>(orow + c * 32 + j) = o;
-            }
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t chunk = uint32_t((c & 1) * 4 + j) ^ uint32_t(row & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rbase + (chunk << 4)),
+                         "r"(pack2_bf16(v[8 * j] * inv, v[8 * j + 1] * inv)), "r"(pack2_bf16(v[8 * j + 2] * inv, v[8 * j + 3] * inv)),
+                         "r"(pack2_bf16(v[8 * j + 4] * inv, v[8 * j + 5] * inv)), "r"(pack2_bf16(v[8 * j + 6] * inv, v[8 * j + 7] * inv))
+                         : "memory");
           }
         }
+        fence_proxy_async();
+      }
+      // every thread of the warpgroup arrives, also one that gave up on a wait: a hardware barrier has no limit
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + h) : "memory");
+      if (ok && quarter == 0 && lane == 0 && !*abort_flag) {
+        tma_store_3d(&map_o, stage, 0, row0, head);
+        tma_store_3d(&map_o, stage + TC_SLAB_BYTES, 64, row0, head);
+        tma_store_commit_and_wait_read();
       }
       if (h == 0 && lane == 0 && quarter == 0) TRACE(2, 63, 5);
     }
@@ -457,10 +471,11 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 // generic kernel).
 int sparse_attention_tc5(const AttnParams& a, int n_kv_heads, cudaStream_t st) {
   if (a.q_sn <= 0 || a.k_sn <= 0 || a.v_sn <= 0 || a.q_sh <= 0 || a.k_sh <= 0 || a.v_sh <= 0) return SPF_ERR_SHAPE;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if (!make_map(&mq, a.q, a.n_tokens, a.n_q_heads, a.q_sn, a.q_sh) ||
       !make_map(&mk, a.k, a.n_tokens, n_kv_heads, a.k_sn, a.k_sh) ||
-      !make_map(&mv, a.v, a.n_tokens, n_kv_heads, a.v_sn, a.v_sh))
+      !make_map(&mv, a.v, a.n_tokens, n_kv_heads, a.v_sn, a.v_sh) ||
+      !make_map(&mo, a.out, a.n_tokens, a.n_q_heads, int64_t(a.n_q_heads) * TC_D, TC_D))
     return SPF_ERR_SHAPE;
   Tc5Params p;
   p.out = a.out; p.bitmap = a.bitmap; p.n_tokens = a.n_tokens; p.n_q_heads = a.n_q_heads;
@@ -470,7 +485,7 @@ int sparse_attention_tc5(const AttnParams& a, int n_kv_heads, cudaStream_t st) {
                                        int(TC_SMEM_TOTAL));
   if (e != cudaSuccess) { note_cuda_error(e); return SPF_ERR_LAUNCH; }
   const unsigned grid = unsigned(n_kv_heads) * (unsigned(a.nb) * unsigned(p.pairs) + ((a.group & 1) ? unsigned(a.nb + 1) / 2u : 0u));
-  sparse_attn_tc5_kernel<<<grid, TC_THREADS, TC_SMEM_TOTAL, st>>>(mq, mk, mv, p);
+  sparse_attn_tc5_kernel<<<grid, TC_THREADS, TC_SMEM_TOTAL, st>>>(mq, mk, mv, mo, p);
   return check_launch();
 }
 

@@ -67,7 +67,7 @@ def test_tc5_matches_oracle_and_generic(n, h, hkv, density):
     for name, got in (("tcgen05", out_tc5), ("generic", out_gen)):
         _assert_out_close(got, want, name)
     d = (out_tc5.float() - out_gen.float()).abs()
-    assert d.max().item() <= MAX_ABS
+    assert bool((d <= torch.maximum(torch.full_like(d, MAX_ABS), out_gen.float().abs() * 2.0 ** -7)).all())
 
 
 @pytest.mark.parametrize("n,h,hkv,density", [

@@ -39,7 +39,8 @@ CHILD = textwrap.dedent("""
     ref = torch.nn.functional.scaled_dot_product_attention(
         q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None], is_causal=True,
         enable_gqa=True)[0].transpose(0, 1)
-    assert (out.float() - ref.float()).abs().max().item() <= 2e-2
+    err = (out.float() - ref.float()).abs()
+    assert bool((err <= torch.maximum(torch.full_like(err, 2e-2), ref.float().abs() * 2.0 ** -7)).all())
     assert native.device_timeouts() == 0
     # more than 16 recorded timeouts: the tcgen05 entry points refuse to launch until the counter is reset
     assert lib.spf_set_device_wait_limit_ns(200_000) == 0
