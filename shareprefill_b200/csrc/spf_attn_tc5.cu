@@ -20,9 +20,11 @@
 //   warp 3      idle (it only completes the control warpgroup, which gives registers to the softmax
 //               warpgroups with setmaxnreg)
 //   warps 4-7   softmax warpgroup of head A: a thread owns one query row; tcgen05.ld of S, base-2
-//               online softmax with scale*log2(e) folded in, P rounded to bf16 and written back
-//               over S with tcgen05.st, O rescaled in TMEM only when the running maximum moved by
-//               more than 2^8 (exact: the final normalisation uses the same reference point)
+//               softmax with scale*log2(e) folded in against a reference point that is the maximum
+//               of the row's first block and moves only when a score lies more than 2^64 above it
+//               (exact: the final normalisation uses the same reference), a quarter of the
+//               exponentials as a polynomial on the FMA pipe, P rounded to bf16 and written back
+//               over S with tcgen05.st
 //   warps 8-11  the same for head B
 //
 // TMEM (512 columns): S_A/P_A [0,128)  S_B/P_B [128,256)  O_A [256,384)  O_B [384,512).
@@ -37,7 +39,7 @@ namespace spf {
 constexpr int TC_THREADS = 384;                             // 3 warpgroups: control, softmax A, softmax B
 // setmaxnreg targets.  The CTA owns the registers it was launched with (384 threads x 168) and no more:
 // a sum beyond that pool would leave the last setmaxnreg.inc waiting for ever.
-constexpr int TC_REGS_CONTROL = 128, TC_REGS_SOFTMAX = 184;
+constexpr int TC_REGS_CONTROL = 104, TC_REGS_SOFTMAX = 200;
 static_assert(4 * TC_REGS_CONTROL + 8 * TC_REGS_SOFTMAX <= 12 * 168, "setmaxnreg targets exceed the CTA's register pool");
 constexpr int TC_KSTAGES = 3;
 constexpr int TC_VSTAGES = 2;
@@ -48,10 +50,12 @@ constexpr uint32_t TC_SMEM_Q = 1024;
 constexpr uint32_t TC_SMEM_K = TC_SMEM_Q + 2 * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_V = TC_SMEM_K + TC_KSTAGES * TC_TILE_BYTES;
 constexpr uint32_t TC_SMEM_TOTAL = TC_SMEM_V + TC_VSTAGES * TC_TILE_BYTES;   // 225 KiB of the 227 KiB limit
-// O is rescaled only when a row's maximum moved by more than this (in log2 units) above the reference
-// point in use; P = 2^(s - reference) then reaches at most 2^24, far inside the range of bf16 and of the
-// fp32 accumulators, and the final normalisation uses the same reference, so the result is exact
-constexpr float TC_RESCALE_LOG2 = 24.0f;
+// The reference point of a row's exponentials moves only when a score lies more than this (in log2
+// units) above it; see the softmax warps
+constexpr float TC_RESCALE_LOG2 = 64.0f;
+constexpr float TC_BLOCK_SUM_LIMIT = 1180591620717411303424.0f;   // 2^70
+// of every 8 pairs of exponentials, this many are computed on the FMA pipe (exp_pack_poly)
+constexpr int TC_POLY_PAIRS = 2;
 // descriptor table: the eight k-step descriptors of Q_A, Q_B, every K stage and every V stage
 constexpr int DT_Q = 0, DT_K = 16, DT_V = DT_K + 8 * TC_KSTAGES, DT_N = DT_V + 8 * TC_VSTAGES;
 static_assert(TC_SMEM_DTAB + DT_N * 8 <= TC_SMEM_Q, "descriptor table does not fit the control region");
@@ -374,20 +378,37 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mask_after(s2, row - 64);
           mask_after(s3, row - 96);
         }
-        const float mx = fmaxf(fmaxf(row_max(s0), row_max(s1)), fmaxf(row_max(s2), row_max(s3)));
-        const float mb = mx * p.scale_log2;
+        // Only a row's first block needs its maximum before the exponentials: it fixes the reference
+        // point m_used.  Later blocks go straight to P = 2^(s*scale - m_used), which keeps the maximum
+        // reduction off the chain S -> P -> next S.  A block whose sum of P comes out above 2^70 (a score
+        // at least 2^63 above the reference - or the sum is not finite) is redone after the reference has
+        // been moved up to its maximum and O rescaled; P, l and O stay far inside the range of bf16 and
+        // fp32, and the final normalisation uses the same reference, so the result does not depend on it.
+        auto row_max_log2 = [&]() {
+          return fmaxf(fmaxf(row_max(s0), row_max(s1)), fmaxf(row_max(s2), row_max(s3))) * p.scale_log2;
+        };
+        // P as bf16 over the first 64 columns of the S region; returns the sum of the unrounded values
+        auto emit_p = [&]() {
+          float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+          uint32_t pk[16];
+          exp_pack_poly<TC_POLY_PAIRS>(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tS + 0, pk);
+          exp_pack_poly<TC_POLY_PAIRS>(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tS + 16, pk);
+          exp_pack_poly<TC_POLY_PAIRS>(s2, p.scale_log2, m_used, pk, l2); tmem_st16(tS + 32, pk);
+          exp_pack_poly<TC_POLY_PAIRS>(s3, p.scale_log2, m_used, pk, l3); tmem_st16(tS + 48, pk);
+          return (l0 + l1) + (l2 + l3);
+        };
+        if (k == 0) m_used = row_max_log2();
         if (lane == 0 && quarter == 0) TRACE(h, k, 5);
-        float alpha = 1.f;
-        bool grow = false;
-        if (k == 0) {
-          m_used = mb;
-        } else if (mb > m_used + TC_RESCALE_LOG2) {
-          alpha = exp2f(m_used - mb);
-          m_used = mb;
-          l_sum *= alpha;
-          grow = true;
-        }
-        if (__any_sync(0xffffffffu, grow)) {
+        float blk = emit_p();
+        if (k > 0 && __any_sync(0xffffffffu, !(blk <= TC_BLOCK_SUM_LIMIT))) {
+          tc_wait_st();
+          const float mb = row_max_log2();
+          float alpha = 1.f;
+          if (mb > m_used + TC_RESCALE_LOG2) {
+            alpha = exp2f(m_used - mb);
+            m_used = mb;
+            l_sum *= alpha;
+          }
           // S_h(k) is complete, hence so is every earlier P V of this head: O_h is stable
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
@@ -397,15 +418,9 @@ sparse_attn_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int j = 0; j < 32; ++j) v[j] *= alpha;
             tmem_st32(tO + c * 32, v);
           }
+          blk = emit_p();
         }
-        // P = 2^(s*scale - m) as bf16 over the first 64 columns of the S region
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-        uint32_t pk[16];
-        exp_pack(s0, p.scale_log2, m_used, pk, l0); tmem_st16(tS + 0, pk);
-        exp_pack(s1, p.scale_log2, m_used, pk, l1); tmem_st16(tS + 16, pk);
-        exp_pack(s2, p.scale_log2, m_used, pk, l2); tmem_st16(tS + 32, pk);
-        exp_pack(s3, p.scale_log2, m_used, pk, l3); tmem_st16(tS + 48, pk);
-        l_sum += (l0 + l1) + (l2 + l3);
+        l_sum += blk;
         if (lane == 0 && quarter == 0) TRACE(h, k, 3);
         tc_wait_st();
         if (lane == 0 && quarter == 0) TRACE(h, k, 6);

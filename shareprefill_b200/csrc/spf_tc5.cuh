@@ -185,6 +185,54 @@ __device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], float scale, f
   sum += a0 + a1;
 }
 
+// The same with POLY of every 8 element pairs taken off the exponential unit (16 exponentials per
+// clock and SM): their 2^y comes from a range reduction and a degree-3 polynomial on the FMA pipe
+// (relative error 7.5e-5, far below the bf16 rounding of P).
+//   u = sat((y + 57) / 128)         y = s*scale - m clamped to [-57, 71]: the reference point m never
+//                                   exceeds the row's true maximum, so 2^-57 is noise against l >= 1
+//   n = round(128u - 57) by the 1.5 * 2^23 trick;  f = 128u - 57 - n in [-0.5, 0.5]
+//   2^y = poly(f) * 2^n             n is added to the exponent field of poly(f)
+template <int POLY>
+__device__ __forceinline__ void exp_pack_poly(const uint32_t (&r)[32], float scale, float m, uint32_t (&pk)[16], float& sum) {
+  const unsigned long long sc2 = f2_pack(scale, scale), nm2 = f2_pack(-m, -m);
+  const float sc128 = scale * 0.0078125f, b128 = (57.f - m) * 0.0078125f;
+  constexpr float MAGIC = 12582912.f - 57.f;      // 1.5 * 2^23 - 57
+  const unsigned long long k128 = f2_pack(128.f, 128.f), kmag = f2_pack(MAGIC, MAGIC), kneg = f2_pack(-1.f, -1.f);
+  const unsigned long long c0 = f2_pack(0.99992806f, 0.99992806f), c1 = f2_pack(0.69326097f, 0.69326097f),
+                           c2 = f2_pack(0.24261113f, 0.24261113f), c3 = f2_pack(0.05517167f, 0.05517167f);
+  unsigned long long acc[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    float p0, p1;
+    if (((j >> 1) & 7) < POLY) {
+      const float u0 = __saturatef(fmaf(__uint_as_float(r[j]), sc128, b128));
+      const float u1 = __saturatef(fmaf(__uint_as_float(r[j + 1]), sc128, b128));
+      const unsigned long long u = f2_pack(u0, u1);
+      const unsigned long long xf = f2_fma(u, k128, kmag);          // MAGIC + n (n in the low mantissa bits)
+      const unsigned long long c = f2_fma(xf, kneg, kmag);          // -(57 + n)
+      const unsigned long long f = f2_fma(u, k128, c);
+      unsigned long long pl = f2_fma(f, c3, c2);
+      pl = f2_fma(pl, f, c1);
+      pl = f2_fma(pl, f, c0);
+      float q0, q1, x0, x1;
+      f2_unpack(pl, q0, q1);
+      f2_unpack(xf, x0, x1);
+      p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(x0) << 23));
+      p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(x1) << 23));
+    } else {
+      const unsigned long long x = f2_pack(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+      float y0, y1;
+      f2_unpack(f2_fma(x, sc2, nm2), y0, y1);
+      p0 = fast_exp2(y0); p1 = fast_exp2(y1);
+    }
+    acc[(j >> 1) & 3] = f2_add(acc[(j >> 1) & 3], f2_pack(p0, p1));
+    pk[j >> 1] = bf16x2_from(p0, p1);
+  }
+  float a0, a1;
+  f2_unpack(f2_add(f2_add(acc[0], acc[1]), f2_add(acc[2], acc[3])), a0, a1);
+  sum += a0 + a1;
+}
+
 // 32 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];

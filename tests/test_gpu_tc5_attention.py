@@ -122,6 +122,32 @@ def test_tc5_large_logits_trigger_rescale():
     _assert_out_close(out, want, "rescale")
 
 
+def test_tc5_reference_point_moves_when_a_block_overflows_it():
+    """A row's exponentials are taken against the maximum of its FIRST block; later blocks whose scores
+    lie 2^70 and more above that point must be caught by the block-sum check and redone against their own
+    maximum, with O rescaled.  Keys of block 0 are tiny, keys of blocks 2 and 5 are aligned with the
+    queries (scores 55 and 90 nats above block 0), the rest is noise."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(11)
+    n, h = 1024, 3                                  # an odd group: head pairs and the two-row CTA
+    e = torch.ones(128) / math.sqrt(128.0)
+    q = (25.0 * e + 0.25 * torch.randn(n, h, 128, generator=g)).bfloat16()
+    k = (0.25 * torch.randn(n, 1, 128, generator=g))
+    k[:128] *= 0.01
+    k[256:384] += 25.0 * e
+    k[640:768] += 40.0 * e
+    k = k.bfloat16()
+    v = torch.randn(n, 1, 128, generator=g).bfloat16()
+    nb = n // 128
+    sets = _random_sets(nb, h, 1.0, g)
+    bm = native.sets_to_bitmap(sets, nb, dev)
+    out = _run(q.to(dev), k.to(dev), v.to(dev), bm, "tc5")
+    assert native.load().spf_device_timeouts() == 0
+    assert bool(torch.isfinite(out.float()).all())
+    want, _ = orc.sparse_attention(q, k, v, sets, torch.zeros(h, dtype=torch.bool), 128)
+    _assert_out_close(out, want, "moved reference")
+
+
 def test_tc5_strided_inputs():
     """[H,N,D]-contiguous tensors seen as [N,H,D] views (head stride N*D) go through TMA unchanged."""
     dev = torch.device("cuda:0")
