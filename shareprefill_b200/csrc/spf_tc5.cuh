@@ -167,26 +167,9 @@ __device__ __forceinline__ uint32_t bf16x2_from(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));   // first source -> upper half
   return d;
 }
-// p = 2^(s*scale - m) for 32 scores: packed to bf16 pairs, unrounded values summed into `sum`
-__device__ __forceinline__ void exp_pack(const uint32_t (&r)[32], float scale, float m, uint32_t (&pk)[16], float& sum) {
-  const unsigned long long sc2 = f2_pack(scale, scale), nm2 = f2_pack(-m, -m);
-  unsigned long long acc[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-  for (int j = 0; j < 32; j += 2) {
-    const unsigned long long x = f2_pack(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-    float y0, y1;
-    f2_unpack(f2_fma(x, sc2, nm2), y0, y1);
-    const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-    acc[(j >> 1) & 3] = f2_add(acc[(j >> 1) & 3], f2_pack(p0, p1));
-    pk[j >> 1] = bf16x2_from(p0, p1);
-  }
-  float a0, a1;
-  f2_unpack(f2_add(f2_add(acc[0], acc[1]), f2_add(acc[2], acc[3])), a0, a1);
-  sum += a0 + a1;
-}
-
-// The same with POLY of every 8 element pairs taken off the exponential unit (16 exponentials per
-// clock and SM): their 2^y comes from a range reduction and a degree-3 polynomial on the FMA pipe
+// p = 2^(s*scale - m) for 32 scores: packed to bf16 pairs, unrounded values summed into `sum`.
+// POLY of every 8 element pairs are taken off the exponential unit (16 exponentials per clock and
+// SM): their 2^y comes from a range reduction and a degree-3 polynomial on the FMA pipe
 // (relative error 7.5e-5, far below the bf16 rounding of P).
 //   u = sat((y + 57) / 128)         y = s*scale - m clamped to [-57, 71]: the reference point m never
 //                                   exceeds the row's true maximum, so 2^-57 is noise against l >= 1
@@ -322,31 +305,6 @@ __device__ __forceinline__ void mma_qk_group(uint32_t d_tmem, uint64_t q_desc, u
       "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, po;\n\t}"
       ::"r"(d_tmem), "l"(q_desc), "l"(k_desc), "r"(TC_IDESC_QK), "n"(STEP), "n"(SLAB) : "memory");
 }
-// O (tmem) (+)= P (tmem, 16 bf16 columns = 8 words per step) V (smem, 16 keys = 2048 bytes per step)
-__device__ __forceinline__ void mma_pv_group(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc, uint32_t acc) {
-  constexpr uint32_t VSTEP = 2048 >> 4;
-  asm volatile(
-      "{\n\t.reg .pred pa, po;\n\t.reg .b32 blo, bhi, ta;\n\t.reg .b64 db;\n\t"
-      "mov.b64 {blo, bhi}, %2;\n\tmov.b32 ta, %1;\n\t"
-      "setp.ne.b32 pa, %4, 0;\n\tsetp.eq.b32 po, 0, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], %2, %3, pa;\n\t"
-      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
-      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
-      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
-      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
-      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
-      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t"
-      "add.u32 ta, ta, 8;\n\tadd.u32 blo, blo, %5;\n\tmov.b64 db, {blo, bhi};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %3, po;\n\t}"
-      ::"r"(o_tmem), "r"(p_tmem), "l"(v_desc), "r"(TC_IDESC_PV), "r"(acc), "n"(VSTEP) : "memory");
-}
-
 // The same products with every descriptor prepared BEFORE the first tcgen05.mma, so that the eight
 // instructions leave the issuing thread back to back (the attention kernel keeps the descriptors of
 // every tile in a shared-memory table).
