@@ -227,12 +227,14 @@ def test_attention_block_and_head_sizes(dev, bs, d):
     _assert_out_close(out, want)
 
 
-def test_full_triangle_equals_dense_causal_at_32k(dev):
-    """Size-independent property at the benchmark's sequence length: with every causal block
-    selected the kernel is plain causal attention (checked against torch SDPA on one KV group)."""
-    wl = WORKLOADS["cfg1"]
+@pytest.mark.parametrize("name,heads", [("cfg1", 4), ("cfg2", 3)])
+def test_full_triangle_equals_dense_causal_at_scale(dev, name, heads):
+    """Size-independent property at the benchmarks' sequence lengths (32K and 128K): with every causal
+    block selected the kernel is plain causal attention (checked against torch SDPA on one KV group;
+    three heads at 128K, so that a head pair and a two-row stream of the odd head both run)."""
+    wl = WORKLOADS[name]
     n, bs = wl.seq_len, wl.block_size
-    q, k, v = make_qkv(wl.replace(num_q_heads=4, num_kv_heads=1), 0, device="cuda")
+    q, k, v = make_qkv(wl.replace(num_q_heads=heads, num_kv_heads=1), 0, device="cuda")
     nb = n // bs
     rows = torch.arange(nb, device=dev)
     words = torch.arange(nb // 32, device=dev)
@@ -240,14 +242,14 @@ def test_full_triangle_equals_dense_causal_at_32k(dev):
     bits = torch.where(last >= 31, torch.full_like(last, 2**32 - 1),
                        torch.where(last < 0, torch.zeros_like(last), (2 << last.clamp(0, 30)) - 1))
     bits = torch.where(bits >= 2**31, bits - 2**32, bits).to(torch.int32)
-    bm = bits[None].expand(4, nb, nb // 32).contiguous()
+    bm = bits[None].expand(heads, nb, nb // 32).contiguous()
     out = native.sparse_attention(q, k, v, bm, bs, 1.0 / math.sqrt(128))
     ref = torch.nn.functional.scaled_dot_product_attention(
         q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None], is_causal=True,
         enable_gqa=True)[0].transpose(0, 1)
     _assert_out_close(out, ref.cpu())
     rows_c, tot = native.bitmap_row_counts(bm)
-    assert tot.tolist() == [nb * (nb + 1) // 2] * 4
+    assert tot.tolist() == [nb * (nb + 1) // 2] * heads
 
 
 def test_selection_invariants_at_32k(dev, tmp_path_factory):
